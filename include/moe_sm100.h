@@ -1,0 +1,170 @@
+/*
+ * moe_sm100.h -- C ABI of libmoe_sm100.so: the top-k mixture-of-experts expert-compute
+ * path of arthurfeeney/moe-explore, written for NVIDIA B200 (sm_100a).
+ *
+ * The reference project has no FFI: its boundary is the Python functional API
+ * (src/moe_explore/functional/topk_moe.py:10-64).  Each entry point below names the
+ * reference function (file:line inside the reference project) whose work it performs;
+ * the Python package `moe_explore` in this repository calls these through ctypes and
+ * keeps the reference's names and signatures.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the comment says "host";
+ *   - the caller owns every allocation; nothing here calls cudaMalloc, except where an
+ *     entry point says otherwise;
+ *   - every launch is asynchronous on `stream` (a cudaStream_t passed as void*);
+ *   - functions return MOE_OK (0) or a negative status; moe_last_error() returns a
+ *     thread-local description of the most recent failure;
+ *   - `dtype` is MOE_DTYPE_BF16 or MOE_DTYPE_F16 (16-bit inputs, fp32 accumulation);
+ *   - `status` (may be NULL) is a device int32 that a kernel sets to a non-zero code when
+ *     one of its bounded waits runs out; the host may read it after synchronising.
+ *
+ * Data layout ("padded expert-sorted rows")
+ *   Routed rows (token t, slot s) have flat position j = t*topk + s.  Rows are stably
+ *   sorted by expert; expert e's rows occupy padded rows [pad_offsets[e], pad_offsets[e+1]),
+ *   a range rounded up to a multiple of MOE_TILE_M so that no 128-row GEMM tile spans two
+ *   experts.  Padding rows hold zeros and have row_src == -1.  Every [RP, *] activation
+ *   buffer uses this layout, RP = moe_padded_rows_bound(R, E).
+ */
+#ifndef MOE_SM100_H_
+#define MOE_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_OK 0
+#define MOE_ERR_INVALID (-1)     /* bad argument (null pointer, negative size, misaligned) */
+#define MOE_ERR_UNSUPPORTED (-2) /* shape or device this library does not handle */
+#define MOE_ERR_CUDA (-3)        /* a CUDA runtime/driver call failed; see moe_last_error() */
+#define MOE_ERR_TIMEOUT (-4)     /* a device-side bounded wait ran out (from moe_check_status) */
+
+#define MOE_DTYPE_BF16 0
+#define MOE_DTYPE_F16 1
+
+#define MOE_ACT_NONE 0
+#define MOE_ACT_SILU 1
+#define MOE_ACT_GELU 2   /* exact erf form */
+#define MOE_ACT_SWIGLU 3 /* silu(even column) * odd column */
+#define MOE_ACT_GEGLU 4  /* gelu(even column) * odd column */
+
+#define MOE_TILE_M 128
+
+/* Thread-local text of the last error reported by this library (never NULL). */
+const char* moe_last_error(void);
+
+/* Device query: SM count and compute capability of `device`.  Replaces
+ * gpu_utils.get_gpu_sm_count (src/moe_explore/gpu_utils.py:4-8).  Returns
+ * MOE_ERR_UNSUPPORTED when the device is not compute capability 10.x. */
+int moe_query_device(int device, int* sm_count, int* cc_major, int* cc_minor);
+
+/* Reads a device status word (synchronises `stream`); MOE_OK or MOE_ERR_TIMEOUT. */
+int moe_check_status(const int32_t* status, void* stream);
+
+/* Upper bounds used to size buffers without reading routing results on the host:
+ * padded row count RP (a multiple of MOE_TILE_M) and number of 128-row tiles. */
+int64_t moe_padded_rows_bound(int64_t num_rows, int num_experts);
+int64_t moe_mtiles_bound(int64_t num_rows, int num_experts);
+
+/* ---------------------------------------------------------------------------------
+ * (a) Routing metadata.  Replaces get_token_indices (src/moe_explore/expert_permute.py:19-41):
+ * argsort of the flattened expert ids, per-expert histogram, prefix sum.  The sort here is
+ * the STABLE counting sort (equal experts keep flat-position order).
+ *   expert_idx    int64 [R]      expert id of flat position j (R = T*topk)
+ *   group_indices int32 [E+1]    exclusive prefix sum of per-expert counts
+ *   perm          int64 [R]      perm[r] = flat position of the r-th row in expert order
+ *   pad_offsets   int32 [E+1]    padded row offset of each expert (multiples of MOE_TILE_M)
+ *   row_src       int32 [RP]     flat position held by padded row p, or -1 for padding
+ *   dst_row       int32 [R]      padded row that holds flat position j (inverse of row_src)
+ *   mtile_expert  int32 [moe_mtiles_bound]  expert of each 128-row tile
+ *   num_mtiles    int32 [1]      number of 128-row tiles in use
+ * Any of perm / row_src / dst_row / mtile_expert+num_mtiles may be NULL to skip it.
+ * ids outside [0, E) are rejected on the device: they are dropped from every output and
+ * `status` is set.  Workspace: moe_routing_workspace_bytes(R, E) bytes.
+ * --------------------------------------------------------------------------------- */
+size_t moe_routing_workspace_bytes(int64_t num_rows, int num_experts);
+int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows, int num_experts,
+                         int32_t* group_indices, int64_t* perm, int32_t* pad_offsets,
+                         int32_t* row_src, int32_t* dst_row, int32_t* mtile_expert,
+                         int32_t* num_mtiles, int32_t* status, void* workspace,
+                         size_t workspace_bytes, void* stream);
+
+/* Same outputs from an existing exclusive prefix `group_indices` [E+1] (rows already in
+ * expert order, identity permutation): used by the plain ragged grouped GEMM
+ * (m_grouped_gemm with gather=scatter=False, triton_kernels/m_grouped_gemm.py:332-393).
+ * row_src[p] is the unpadded row index. */
+int moe_layout_from_groups(const int32_t* group_indices, int64_t num_rows, int num_experts,
+                           int32_t* pad_offsets, int32_t* row_src, int32_t* dst_row,
+                           int32_t* mtile_expert, int32_t* num_mtiles, void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * Row movement (HBM-bound).  Replace row_gather / row_scatter
+ * (triton_kernels/row_gather_scatter.py:36-116) and scale_and_reduce
+ * (functional/scale_and_reduce.py:3-5).
+ * --------------------------------------------------------------------------------- */
+
+/* dst[p, :] = src[row_src[p] / div, :] for padded rows p < 128*num_mtiles, zeros where
+ * row_src[p] < 0.  div = topk gathers token rows; div = 1 gathers flat-position rows. */
+int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src,
+                    const int32_t* num_mtiles, void* dst, int64_t padded_rows, int cols,
+                    int div, int dtype, void* stream);
+
+/* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order. */
+int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows,
+                   int cols, int dtype, void* stream);
+
+/* out[t, :] = sum_s scale(t,s) * ys[dst_row[t*topk+s], :], fp32 accumulation, one rounding.
+ * scores: [T, topk] in `dtype`, or NULL for scale 1 (used for dX). */
+int moe_combine_topk(const void* ys, const void* scores, const int32_t* dst_row, void* out,
+                     int64_t num_tokens, int topk, int cols, int dtype, void* stream);
+
+/* Backward of the combine: for padded row p holding flat position j = (t, s):
+ *   gs[p, :]   = scores[j] * dout[t, :]
+ *   dscores[j] = dot(dout[t, :], ys[p, :])      (fp32 accumulation, stored in `dtype`)
+ * padding rows of gs are zeroed. */
+int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
+                    const int32_t* row_src, const int32_t* num_mtiles, void* gs, void* dscores,
+                    int64_t num_tokens, int topk, int64_t padded_rows, int cols, int dtype,
+                    void* stream);
+
+/* ---------------------------------------------------------------------------------
+ * (b),(c),(d) Grouped GEMMs on tcgen05 tensor cores (TMA operand tiles, TMEM accumulators,
+ * persistent tile loop).  Replace m_grouped_gemm and its fused epilogues
+ * (triton_kernels/m_grouped_gemm.py:33-267, epilogue_split.py:4-44,
+ * triton_kernels/activation.py:5-36).  All row counts are in the padded layout.
+ * Requirements: every column count a multiple of 8; pointers 16-byte aligned.
+ * --------------------------------------------------------------------------------- */
+
+/* M-grouped: out = epilogue(a[rows of tile] @ w[expert of tile]).
+ *   a    [RP, K]
+ *   w    [E, K, N] when w_transposed == 0, [E, N, K] when w_transposed == 1
+ *   act  MOE_ACT_NONE/SILU/GELU: out [RP, N];  MOE_ACT_SWIGLU/GEGLU: out [RP, N/2] and,
+ *        when pre_act != NULL, pre_act [RP, N] receives the un-activated product. */
+int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act,
+                      const int32_t* mtile_expert, const int32_t* num_mtiles,
+                      int64_t padded_rows, int K, int N, int num_experts, int w_transposed,
+                      int act, int dtype, int32_t* status, void* stream);
+
+/* Backward through the GLU: d_pre[RP, 2N] = dGLU(pre_act[RP, 2N]) * (g[RP, K] @ w[E, N, K]^T),
+ * i.e. for the layer: g = score-scaled dOut rows, w = weight2 [E, I, d] (N = I, K = d),
+ * pre_act = the saved gate/up product.  act must be MOE_ACT_SWIGLU or MOE_ACT_GEGLU.
+ * No counterpart in the reference (it has no backward). */
+int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, void* d_pre,
+                           const int32_t* mtile_expert, const int32_t* num_mtiles,
+                           int64_t padded_rows, int K, int N, int num_experts, int act,
+                           int dtype, int32_t* status, void* stream);
+
+/* K-grouped (expert weight gradients): dw[e] = a[rows of e]^T @ b[rows of e],
+ *   a [RP, M], b [RP, N], dw [E, M, N]; experts without rows get zeros.
+ * No counterpart in the reference (it has no backward). */
+int moe_kgrouped_gemm(const void* a, const void* b, void* dw, const int32_t* pad_offsets,
+                      int64_t padded_rows, int M, int N, int num_experts, int dtype,
+                      int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_SM100_H_ */

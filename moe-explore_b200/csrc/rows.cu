@@ -1,0 +1,212 @@
+// Row movement around the grouped GEMMs: gather token rows into the padded expert-sorted
+// layout, fold the top-k slots back into token order with the router weights, and the
+// backward of that fold.  All kernels are HBM-bound: 16-byte vector accesses, one warp per
+// row segment, fp32 accumulation where values are summed.
+//
+// Replace row_gather / row_scatter (reference: src/moe_explore/triton_kernels/row_gather_scatter.py:36-116)
+// and scale_and_reduce (src/moe_explore/functional/scale_and_reduce.py:3-5).
+#include "common.cuh"
+
+namespace moe {
+
+constexpr int kRowThreads = 256;
+
+// dst[p, :] = src[row_src[p] / div, :], zeros for padding rows.  One CTA per padded row.
+__global__ void __launch_bounds__(kRowThreads)
+gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ row_src,
+                   const int32_t* __restrict__ num_mtiles, uint4* __restrict__ dst, int vec_per_row, int div) {
+  const int64_t rows_in_use = static_cast<int64_t>(*num_mtiles) * MOE_TILE_M;
+  for (int64_t p = blockIdx.x; p < rows_in_use; p += gridDim.x) {
+    const int32_t j = row_src[p];
+    uint4* d = dst + p * vec_per_row;
+    if (j < 0) {
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = make_uint4(0, 0, 0, 0);
+    } else {
+      const uint4* s = src + static_cast<int64_t>(j / div) * vec_per_row;
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = s[v];
+    }
+  }
+}
+
+// out[j, :] = src[dst_row[j], :]
+__global__ void __launch_bounds__(kRowThreads)
+unpad_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ dst_row, uint4* __restrict__ out,
+                  int64_t num_rows, int vec_per_row) {
+  for (int64_t j = blockIdx.x; j < num_rows; j += gridDim.x) {
+    const uint4* s = src + static_cast<int64_t>(dst_row[j]) * vec_per_row;
+    uint4* d = out + j * vec_per_row;
+    for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = s[v];
+  }
+}
+
+template <typename T>
+__device__ __forceinline__ void fma8(float (&acc)[8], const uint4& u, float scale) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = Elem<T>::unpack2(w[i]);
+    acc[2 * i] = fmaf(scale, f.x, acc[2 * i]);
+    acc[2 * i + 1] = fmaf(scale, f.y, acc[2 * i + 1]);
+  }
+}
+
+// out[t, :] = sum_s scale(t, s) * ys[dst_row[t*topk + s], :]
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+combine_topk_kernel(const uint4* __restrict__ ys, const T* __restrict__ scores, const int32_t* __restrict__ dst_row,
+                    uint4* __restrict__ out, int64_t num_tokens, int topk, int vec_per_row) {
+  for (int64_t t = blockIdx.x; t < num_tokens; t += gridDim.x) {
+    for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int s = 0; s < topk; ++s) {
+        const int64_t j = t * topk + s;
+        const float scale = scores != nullptr ? Elem<T>::to_float(scores[j]) : 1.0f;
+        const uint4 u = ys[static_cast<int64_t>(dst_row[j]) * vec_per_row + v];
+        fma8<T>(acc, u, scale);
+      }
+      uint4 r;
+      r.x = Elem<T>::pack2(acc[0], acc[1]);
+      r.y = Elem<T>::pack2(acc[2], acc[3]);
+      r.z = Elem<T>::pack2(acc[4], acc[5]);
+      r.w = Elem<T>::pack2(acc[6], acc[7]);
+      out[t * vec_per_row + v] = r;
+    }
+  }
+}
+
+// gs[p, :] = scores[j] * dout[t, :];  dscores[j] = dot(dout[t, :], ys[p, :]);  j = row_src[p], t = j / topk
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+combine_bwd_kernel(const uint4* __restrict__ dout, const T* __restrict__ scores, const uint4* __restrict__ ys,
+                   const int32_t* __restrict__ row_src, const int32_t* __restrict__ num_mtiles,
+                   uint4* __restrict__ gs, T* __restrict__ dscores, int topk, int vec_per_row) {
+  __shared__ float partial[kRowThreads / 32];
+  const int64_t rows_in_use = static_cast<int64_t>(*num_mtiles) * MOE_TILE_M;
+  for (int64_t p = blockIdx.x; p < rows_in_use; p += gridDim.x) {
+    const int32_t j = row_src[p];
+    uint4* g = gs + p * vec_per_row;
+    if (j < 0) {
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) g[v] = make_uint4(0, 0, 0, 0);
+      continue;  // uniform across the CTA
+    }
+    const float scale = Elem<T>::to_float(scores[j]);
+    const uint4* d = dout + static_cast<int64_t>(j / topk) * vec_per_row;
+    const uint4* y = ys + p * vec_per_row;
+    float dot = 0.0f;
+    for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+      const uint4 du = d[v];
+      const uint4 yu = y[v];
+      const uint32_t dw[4] = {du.x, du.y, du.z, du.w};
+      const uint32_t yw[4] = {yu.x, yu.y, yu.z, yu.w};
+      uint32_t ow[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 df = Elem<T>::unpack2(dw[i]);
+        const float2 yf = Elem<T>::unpack2(yw[i]);
+        dot = fmaf(df.x, yf.x, dot);
+        dot = fmaf(df.y, yf.y, dot);
+        ow[i] = Elem<T>::pack2(scale * df.x, scale * df.y);
+      }
+      g[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
+    __syncthreads();  // previous iteration's readers of `partial` are done
+    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = dot;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < kRowThreads / 32; ++w) total += partial[w];
+      dscores[j] = Elem<T>::from_float(total);
+    }
+  }
+}
+
+static int row_grid(int64_t rows) {
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
+  return static_cast<int>(rows < cap ? (rows > 0 ? rows : 1) : cap);
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace moe
+
+using namespace moe;
+
+#define MOE_ROW_COMMON_CHECKS(name, cols, dtype)                                                          \
+  MOE_CHECK_ARG((cols) > 0, name ": cols=%d must be positive", (cols));                                  \
+  if ((cols) % 8 != 0) {                                                                                 \
+    set_error(name ": cols=%d must be a multiple of 8 (16-byte rows)", (cols));                          \
+    return MOE_ERR_UNSUPPORTED;                                                                          \
+  }                                                                                                      \
+  MOE_CHECK_ARG((dtype) == MOE_DTYPE_BF16 || (dtype) == MOE_DTYPE_F16, name ": unknown dtype %d", (dtype))
+
+extern "C" int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src, const int32_t* num_mtiles,
+                               void* dst, int64_t padded_rows, int cols, int div, int dtype, void* stream) {
+  MOE_CHECK_ARG(src && row_src && num_mtiles && dst, "moe_gather_rows: null pointer argument");
+  MOE_CHECK_ARG(aligned16(src) && aligned16(dst), "moe_gather_rows: pointers must be 16-byte aligned");
+  MOE_CHECK_ARG(src_rows >= 0 && padded_rows > 0 && div > 0, "moe_gather_rows: bad sizes");
+  MOE_ROW_COMMON_CHECKS("moe_gather_rows", cols, dtype);
+  gather_rows_kernel<<<row_grid(padded_rows), kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), row_src, num_mtiles, static_cast<uint4*>(dst), cols / 8, div);
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}
+
+extern "C" int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows, int cols, int dtype,
+                              void* stream) {
+  MOE_CHECK_ARG(num_rows >= 0, "moe_unpad_rows: num_rows is negative");
+  if (num_rows == 0) return MOE_OK;
+  MOE_CHECK_ARG(src && dst_row && out, "moe_unpad_rows: null pointer argument");
+  MOE_CHECK_ARG(aligned16(src) && aligned16(out), "moe_unpad_rows: pointers must be 16-byte aligned");
+  MOE_ROW_COMMON_CHECKS("moe_unpad_rows", cols, dtype);
+  unpad_rows_kernel<<<row_grid(num_rows), kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), dst_row, static_cast<uint4*>(out), num_rows, cols / 8);
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}
+
+extern "C" int moe_combine_topk(const void* ys, const void* scores, const int32_t* dst_row, void* out,
+                                int64_t num_tokens, int topk, int cols, int dtype, void* stream) {
+  MOE_CHECK_ARG(num_tokens >= 0 && topk > 0, "moe_combine_topk: bad sizes T=%lld topk=%d", (long long)num_tokens, topk);
+  if (num_tokens == 0) return MOE_OK;
+  MOE_CHECK_ARG(ys && dst_row && out, "moe_combine_topk: null pointer argument");
+  MOE_CHECK_ARG(aligned16(ys) && aligned16(out), "moe_combine_topk: pointers must be 16-byte aligned");
+  MOE_ROW_COMMON_CHECKS("moe_combine_topk", cols, dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = row_grid(num_tokens);
+  if (dtype == MOE_DTYPE_BF16) {
+    combine_topk_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(
+        static_cast<const uint4*>(ys), static_cast<const __nv_bfloat16*>(scores), dst_row, static_cast<uint4*>(out),
+        num_tokens, topk, cols / 8);
+  } else {
+    combine_topk_kernel<__half><<<grid, kRowThreads, 0, s>>>(static_cast<const uint4*>(ys),
+                                                             static_cast<const __half*>(scores), dst_row,
+                                                             static_cast<uint4*>(out), num_tokens, topk, cols / 8);
+  }
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}
+
+extern "C" int moe_combine_bwd(const void* dout, const void* scores, const void* ys, const int32_t* row_src,
+                               const int32_t* num_mtiles, void* gs, void* dscores, int64_t num_tokens, int topk,
+                               int64_t padded_rows, int cols, int dtype, void* stream) {
+  MOE_CHECK_ARG(dout && scores && ys && row_src && num_mtiles && gs && dscores, "moe_combine_bwd: null pointer argument");
+  MOE_CHECK_ARG(aligned16(dout) && aligned16(ys) && aligned16(gs), "moe_combine_bwd: pointers must be 16-byte aligned");
+  MOE_CHECK_ARG(num_tokens >= 0 && topk > 0 && padded_rows > 0, "moe_combine_bwd: bad sizes");
+  MOE_ROW_COMMON_CHECKS("moe_combine_bwd", cols, dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = row_grid(padded_rows);
+  if (dtype == MOE_DTYPE_BF16) {
+    combine_bwd_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(
+        static_cast<const uint4*>(dout), static_cast<const __nv_bfloat16*>(scores), static_cast<const uint4*>(ys),
+        row_src, num_mtiles, static_cast<uint4*>(gs), static_cast<__nv_bfloat16*>(dscores), topk, cols / 8);
+  } else {
+    combine_bwd_kernel<__half><<<grid, kRowThreads, 0, s>>>(
+        static_cast<const uint4*>(dout), static_cast<const __half*>(scores), static_cast<const uint4*>(ys), row_src,
+        num_mtiles, static_cast<uint4*>(gs), static_cast<__half*>(dscores), topk, cols / 8);
+  }
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}

@@ -1,0 +1,84 @@
+"""The differentiable expert-compute step of the MoE layer on the native kernels.
+
+forward : gather token rows into the padded expert-sorted layout -> gate/up grouped GEMM with a
+          fused GLU epilogue -> down grouped GEMM -> weighted fold of the top-k slots.
+backward: score-scaled gather of dOut (+ router-weight gradient as a row dot product) ->
+          grouped GEMM against W2^T with the GLU derivative fused -> grouped GEMM against W1^T
+          and an unweighted fold for dX -> two K-grouped GEMMs for the expert weight gradients.
+
+The reference's forward is topk_moe_forward (src/moe_explore/functional/topk_moe.py:16-54);
+it has no backward.  The gradients follow from out[t] = sum_s score[t,s] * (act(x_t W1[e]) W2[e]).
+"""
+from __future__ import annotations
+
+import torch
+
+from moe_explore import _native
+from moe_explore.functional.activation import is_glu
+from moe_explore.routing_plan import RoutingPlan
+
+
+class ExpertCompute(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scores, weight1, weight2, plan: RoutingPlan, act: str):
+        _native.require_cuda(x, scores, weight1, weight2)
+        assert x.dim() == 2 and weight1.dim() == 3 and weight2.dim() == 3
+        T, d = x.shape
+        E, d1, n1 = weight1.shape
+        inter = weight2.size(1)
+        assert d1 == d and weight2.size(0) == E and weight2.size(2) == d, "weight shapes do not match the input"
+        assert n1 == (2 * inter if is_glu(act) else inter), "weight1 width does not match weight2 and the activation"
+        assert plan.num_rows == T * plan.topk and plan.num_experts == E
+        x = x.contiguous()
+        scores = scores.to(x.dtype).contiguous()
+        weight1 = weight1.contiguous()
+        weight2 = weight2.contiguous()
+        rp = plan.padded_rows
+        new = lambda *shape: torch.empty(*shape, dtype=x.dtype, device=x.device)
+
+        xs = new(rp, d)
+        _native.gather_rows(x, plan.row_src, plan.num_mtiles, xs, plan.topk)
+        hidden = new(rp, inter)
+        pre_act = new(rp, n1) if is_glu(act) else None
+        _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.num_mtiles, False, act, plan.status)
+        ys = new(rp, d)
+        _native.mgrouped_gemm(hidden, weight2, ys, None, plan.mtile_expert, plan.num_mtiles, False, None, plan.status)
+        out = new(T, d)
+        _native.combine_topk(ys, scores, plan.dst_row, out, plan.topk)
+
+        ctx.plan = plan
+        ctx.act = act
+        ctx.save_for_backward(xs, pre_act, hidden, ys, scores, weight1, weight2)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        xs, pre_act, hidden, ys, scores, weight1, weight2 = ctx.saved_tensors
+        plan: RoutingPlan = ctx.plan
+        act = ctx.act
+        if not is_glu(act):
+            raise NotImplementedError("backward is implemented for the gated activations (swiglu, geglu)")
+        T, d = grad_out.shape
+        rp = plan.padded_rows
+        grad_out = grad_out.contiguous()
+        new = lambda *shape: torch.empty(*shape, dtype=xs.dtype, device=xs.device)
+
+        gs = new(rp, d)
+        d_scores = new(T, plan.topk)
+        _native.combine_bwd(grad_out, scores, ys, plan.row_src, plan.num_mtiles, gs, d_scores, plan.topk)
+        d_pre = new(rp, pre_act.size(1))
+        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.num_mtiles, act, plan.status)
+        dxs = new(rp, d)
+        _native.mgrouped_gemm(d_pre, weight1, dxs, None, plan.mtile_expert, plan.num_mtiles, True, None, plan.status)
+        dx = new(T, d)
+        _native.combine_topk(dxs, None, plan.dst_row, dx, plan.topk)
+        d_w1 = torch.empty_like(weight1)
+        _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status)
+        d_w2 = torch.empty_like(weight2)
+        _native.kgrouped_gemm(hidden, gs, d_w2, plan.pad_offsets, plan.status)
+        return dx, d_scores, d_w1, d_w2, None, None
+
+
+def expert_compute(x, scores, weight1, weight2, plan: RoutingPlan, act) -> torch.Tensor:
+    """out[t] = sum_s scores[t,s] * (act(x[t] @ weight1[e]) @ weight2[e]),  e = expert of (t, s)."""
+    return ExpertCompute.apply(x, scores, weight1, weight2, plan, None if act is None else str(act))
