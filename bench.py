@@ -1,0 +1,490 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE layer forward + backward on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one forward + backward pass of the layer (router -> routing metadata -> expert
+compute -> gradients of input, router weight and both expert weight tensors) over one batch of
+seeded synthetic tokens.  N = 1 runs the Mixtral-8x7B-shaped layer; N > 1 runs the
+DeepSeek-V3-shaped expert-parallel layer, experts sharded over the ranks (launch with torchrun).
+Rank 0 prints ONE JSON line.
+
+``--impl reference`` times the reference algorithm's CPU restatement (oracle/moe_oracle.py, fp32,
+all host threads) on a bounded token sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "moe-explore_b200"))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: T (per GPU), d, E, k, I, router
+    "mixtral_8x7b": dict(T=8192, d=4096, E=8, k=2, I=14336, router="linear"),
+    "qwen15_moe_a27b": dict(T=16384, d=2048, E=60, k=4, I=1408, router="logits_bias"),
+    "deepseek_v3_ep": dict(T=32768, d=7168, E=256, k=8, I=2048, router="zipf"),
+    "olmoe_8192": dict(T=8192, d=2048, E=64, k=8, I=1024, router="logits"),
+}
+METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+
+
+def algorithmic_flops(w, tokens, with_router):
+    """18*R*d*I for the six expert contractions (+ 6*T*d*E when a router linear layer is timed)."""
+    f = 18.0 * tokens * w["k"] * w["d"] * w["I"]
+    if with_router:
+        f += 6.0 * tokens * w["d"] * w["E"]
+    return f
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            p = json.load(open(path))
+            return dict(source="measured", burst=float(p["bf16_tflops"]), sustained=float(p["bf16_tflops_sustained"]),
+                        hbm=float(p["hbm_gbs"]))
+        except Exception:
+            pass
+    return dict(source="fallback", burst=1590.0, sustained=1400.0, hbm=6650.0)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu_index), "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax = float(parts[2])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return dict(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=smax, reasons=sorted(reasons), samples=len(sm))
+
+
+# ----------------------------------------------------------------------------------------------
+# synthetic inputs
+# ----------------------------------------------------------------------------------------------
+def make_logits(w, T, gen, device, rank=0):
+    """Router logits for the workloads that supply them directly (no router GEMM in the step)."""
+    E = w["E"]
+    if w["router"] == "logits":
+        return torch.randn(T, E, generator=gen, device=device)
+    if w["router"] == "logits_bias":
+        bias = torch.randn(E, generator=gen, device=device) * 0.5
+        return torch.randn(T, E, generator=gen, device=device) + bias
+    if w["router"] == "zipf":
+        # popularity ~ rank^-1.1 over a random expert permutation (same permutation on every rank);
+        # log p + Gumbel noise, so the top-k is a sample without replacement proportional to p
+        pg = torch.Generator(device=device).manual_seed(1234)
+        p = torch.arange(1, E + 1, dtype=torch.float32, device=device) ** -1.1
+        p = (p / p.sum())[torch.randperm(E, generator=pg, device=device)]
+        u = torch.rand(T, E, generator=gen, device=device).clamp_min(1e-20)
+        return torch.log(p) - torch.log(-torch.log(u))
+    raise ValueError(w["router"])
+
+
+def make_inputs(w, device, rank=0, world=1, dtype=torch.bfloat16):
+    """x ~ N(0,1); weights ~ N(0,0.02); gate/up drawn separately and interleaved (even = gate)."""
+    from moe_explore.params import interleave_gate_up
+
+    T, d, E, k, I = w["T"], w["d"], w["E"], w["k"], w["I"]
+    gen = torch.Generator(device=device).manual_seed(rank)
+    x = torch.randn(T, d, generator=gen, device=device).to(dtype)
+    grad_out = torch.randn(T, d, generator=gen, device=device).to(dtype)
+    e_local = E // world
+    wgen = torch.Generator(device=device).manual_seed(1000 + rank)
+
+    def normal(*shape):
+        out = torch.empty(*shape, dtype=dtype, device=device)
+        for e in range(shape[0]):  # per expert, to bound the fp32 temporary
+            out[e] = (torch.randn(*shape[1:], generator=wgen, device=device) * 0.02).to(dtype)
+        return out
+
+    gate, up = normal(e_local, d, I), normal(e_local, d, I)
+    w1 = interleave_gate_up(gate, up)
+    del gate, up
+    w2 = normal(e_local, I, d)
+    router_weight, logits = None, None
+    if w["router"] == "linear":
+        rg = torch.Generator(device=device).manual_seed(77)
+        router_weight = (torch.randn(d, E, generator=rg, device=device) * 0.02).to(dtype)
+    else:
+        logits = make_logits(w, T, gen, device, rank)
+    return dict(x=x, grad_out=grad_out, w1=w1, w2=w2, router_weight=router_weight, logits=logits)
+
+
+# ----------------------------------------------------------------------------------------------
+# our arm
+# ----------------------------------------------------------------------------------------------
+def scores_from_logits(logits, k, dtype):
+    top, idx = torch.topk(logits, k, dim=-1, sorted=False)
+    return torch.softmax(top, dim=-1, dtype=torch.float32).to(dtype), idx
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    from moe_explore import _native
+    from moe_explore.functional.topk_moe import topk_moe_forward
+    from moe_explore.params import MLPParams, MOEParams, TopkRouterParams
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    _native.load()
+    _native.query_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    name = args.workload or ("mixtral_8x7b" if world == 1 else "deepseek_v3_ep")
+    w = WORKLOADS[name]
+    inp = make_inputs(w, device, rank, world)
+    with_router = inp["router_weight"] is not None
+    x, grad_out = inp["x"], inp["grad_out"]
+    w1 = inp["w1"].requires_grad_()
+    w2 = inp["w2"].requires_grad_()
+    if with_router:
+        inp["router_weight"].requires_grad_()
+
+    if world > 1:
+        from moe_explore.expert_parallel import ep_expert_compute
+
+    def step(x_in, g_in):
+        """One forward + backward on device-resident inputs; returns (out, dx)."""
+        x_in.requires_grad_(True)
+        x_in.grad = None
+        if world == 1:
+            if with_router:
+                params = MOEParams(TopkRouterParams(inp["router_weight"], w["k"], False, False),
+                                   MLPParams(w1, w2, "swiglu"), w["E"], w["k"])
+                out = topk_moe_forward(x_in, params)
+            else:
+                from moe_explore.expert_compute import expert_compute
+                from moe_explore.routing_plan import build_routing_plan
+
+                logits = inp["logits"].requires_grad_()
+                scores, idx = scores_from_logits(logits, w["k"], x_in.dtype)
+                plan = build_routing_plan(idx, w["E"], w["k"], want_perm=False)
+                out = expert_compute(x_in, scores, w1, w2, plan, "swiglu")
+        else:
+            logits = inp["logits"].requires_grad_()
+            scores, idx = scores_from_logits(logits, w["k"], x_in.dtype)
+            out = ep_expert_compute(x_in, scores, idx, w1, w2, w["E"], "swiglu")
+        out.backward(g_in)
+        dx = x_in.grad
+        x_in.requires_grad_(False)
+        w1.grad = None
+        w2.grad = None
+        return out.detach(), dx
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing ----
+    for _ in range(max(args.warmup, 3)):
+        step(x, grad_out)
+    sync_all()
+    _native.LAUNCHES = 0
+    _native.PROFILE = {}
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync_all()
+    e0.record()
+    for _ in range(args.steps):
+        step(x, grad_out)
+    e1.record()
+    sync_all()
+    ms = e0.elapsed_time(e1) / args.steps
+    launches = _native.LAUNCHES
+    profile = _native.PROFILE
+    _native.PROFILE = None
+    clocks = sampler.stop() if rank == 0 else None
+    status_ok = True
+
+    # ---- end to end: pinned host buffers in, results read back, every step ----
+    hx = torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(x)
+    hg = torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(grad_out)
+    h_out = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for _ in range(2)]
+    h_dx = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for _ in range(2)]
+    dev_x = [torch.empty_like(x) for _ in range(2)]
+    dev_g = [torch.empty_like(x) for _ in range(2)]
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    main = torch.cuda.current_stream()
+
+    def e2e_loop(n):
+        """Double-buffered: the upload of step i+1 and the read-back of step i-1 overlap step i's compute."""
+        in_ready = [torch.cuda.Event(), torch.cuda.Event()]
+        out_done = [torch.cuda.Event(), torch.cuda.Event()]
+        comp_done = [torch.cuda.Event(), torch.cuda.Event()]
+        with torch.cuda.stream(copy_in):
+            dev_x[0].copy_(hx, non_blocking=True)
+            dev_g[0].copy_(hg, non_blocking=True)
+            in_ready[0].record(copy_in)
+        keep = []
+        for i in range(n):
+            b = i & 1
+            if i + 1 < n:
+                with torch.cuda.stream(copy_in):
+                    copy_in.wait_event(comp_done[b ^ 1]) if i >= 1 else None  # buffer b^1 free once step i-1 computed
+                    dev_x[b ^ 1].copy_(hx, non_blocking=True)
+                    dev_g[b ^ 1].copy_(hg, non_blocking=True)
+                    in_ready[b ^ 1].record(copy_in)
+            main.wait_event(in_ready[b])
+            out, dx = step(dev_x[b], dev_g[b])
+            comp_done[b].record(main)
+            keep.append((out, dx))
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(comp_done[b])
+                h_out[b].copy_(out, non_blocking=True)
+                h_dx[b].copy_(dx, non_blocking=True)
+                out_done[b].record(copy_out)
+            if len(keep) > 2:
+                keep.pop(0)
+        copy_out.synchronize()
+
+    e2e_loop(3)
+    sync_all()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    e2e_loop(args.steps)
+    t1.record()
+    sync_all()
+    e2e_ms = t0.elapsed_time(t1) / args.steps
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        tokens = w["T"] * world
+        flops = algorithmic_flops(w, tokens, with_router)
+        line = {
+            "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "tflops": flops / (ms * 1e-3) / 1e12,
+            "frac_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["burst"],
+            "config": {"workload": name, "tokens_per_gpu": w["T"], "hidden": w["d"], "experts": w["E"], "topk": w["k"],
+                       "intermediate": w["I"], "router": w["router"], "parallelism": f"ep{world}" if world > 1 else "single",
+                       "l2": "inputs larger than L2 (expert weights are re-read from HBM every step)",
+                       "flops_per_step": flops},
+            "clocks": clocks,
+            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 2 * x.numel() * x.element_size() * world,
+                    "d2h_bytes_per_step": 2 * x.numel() * x.element_size() * world},
+            "gpu_launches": launches,
+        }
+        # roofline of the dominant kernel: the gate/up grouped GEMM (4*R*d*I FLOPs per launch)
+        dom = profile.get("mgrouped_gemm:glu") if profile else None
+        if dom:
+            torch.cuda.synchronize()
+            durs = [a.elapsed_time(b) for a, b in dom]
+            avg = sum(durs) / len(durs)
+            rows_local = w["T"] * w["k"]  # mean routed rows per GPU
+            kflops = 4.0 * rows_local * w["d"] * w["I"]
+            ach = kflops / (avg * 1e-3) / 1e12
+            line["roofline"] = {"kernel": "grouped_gemm_kernel<gate/up, SwiGLU epilogue>", "bound": "tensor",
+                                "achieved": ach, "peak": peaks["sustained"], "unit": "TFLOP/s",
+                                "frac": ach / peaks["sustained"], "peak_source": peaks["source"] + " (sustained)",
+                                "frac_of_burst_peak": ach / peaks["burst"], "avg_launch_ms": avg,
+                                "launches_timed": len(durs), "traffic": TRAFFIC_BYTES.get(name)}
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(w, inp, budget_s=20.0)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu capture summarised
+# under profiles/ (null where no capture has been taken for that workload).
+TRAFFIC_BYTES = {}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the oracle on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_step(xs, scores, idx, w1, w2, grad):
+    from oracle import moe_oracle as O
+
+    for t in (xs, scores, w1, w2):
+        t.grad = None
+    out = O.expert_compute(xs, scores, idx, w1, w2, "swiglu")
+    out.backward(grad)
+    return out
+
+
+def cpu_sample_inputs(w, inp, t_cpu):
+    """First t_cpu tokens of the workload, same weights, upcast to fp32 on the host."""
+    x = inp["x"][:t_cpu].float().cpu().requires_grad_()
+    grad = inp["grad_out"][:t_cpu].float().cpu()
+    if inp["router_weight"] is not None:
+        logits = (inp["x"][:t_cpu] @ inp["router_weight"]).float().cpu()
+    else:
+        logits = inp["logits"][:t_cpu].float().cpu()
+    top, idx = torch.topk(logits, w["k"], dim=-1, sorted=False)
+    scores = torch.softmax(top, -1).requires_grad_()
+    return x, scores, idx, grad
+
+
+def cpu_baseline(w, inp, budget_s):
+    """Oracle forward+backward on the host, fp32, all threads, on a token sample sized to ~budget_s."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    w1 = inp["w1"].detach().float().cpu().requires_grad_()
+    w2 = inp["w2"].detach().float().cpu().requires_grad_()
+    t_cpu = min(64, w["T"])
+    xs = cpu_sample_inputs(w, inp, t_cpu)
+    t0 = time.perf_counter()
+    cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
+    probe = time.perf_counter() - t0
+    # grow the sample while two timed passes are expected to fit the budget
+    while t_cpu * 2 <= min(w["T"], 2048) and probe * 2 * 2 < budget_s / 2:
+        t_cpu *= 2
+        probe *= 2
+    xs = cpu_sample_inputs(w, inp, t_cpu)
+    cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])  # warm-up
+    best = 1e30
+    for _ in range(2):
+        t0 = time.perf_counter()
+        cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
+        best = min(best, time.perf_counter() - t0)
+    return {"value": t_cpu / best, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"first {t_cpu} of {w['T']} tokens, all {w['E']} experts' full-size weights, fp32, "
+                      f"oracle forward+backward, best of 2 after 1 warm-up ({best * 1e3:.0f} ms)"}
+
+
+def run_reference(args):
+    """The reference algorithm's CPU restatement, timed on the host cores (rank 0 only)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    world = args.gpus
+    name = args.workload or ("mixtral_8x7b" if world == 1 else "deepseek_v3_ep")
+    w = dict(WORKLOADS[name])
+    torch.set_num_threads(os.cpu_count() or 1)
+    torch.manual_seed(0)
+    T, d, E, k, I = w["T"], w["d"], w["E"], w["k"], w["I"]
+    # Per-step sample: a token subset against the full-size weights of every expert.
+    per_step_budget = 150.0 / (args.steps + args.warmup)
+    w1 = torch.empty(E, d, 2 * I)
+    w2 = torch.empty(E, I, d)
+    for e in range(E):
+        w1[e].normal_(0, 0.02)
+        w2[e].normal_(0, 0.02)
+    w1.requires_grad_()
+    w2.requires_grad_()
+
+    def sample(t_cpu):
+        x = torch.randn(t_cpu, d).requires_grad_()
+        grad = torch.randn(t_cpu, d)
+        top, idx = torch.topk(torch.randn(t_cpu, E), k, dim=-1, sorted=False)
+        return x, torch.softmax(top, -1).requires_grad_(), idx, grad
+
+    t_cpu = min(64, T)
+    xs = sample(t_cpu)
+    t0 = time.perf_counter()
+    cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
+    probe = time.perf_counter() - t0
+    while t_cpu * 2 <= min(T, 4096) and probe * 2 < per_step_budget:
+        t_cpu *= 2
+        probe *= 2
+    xs = sample(t_cpu)
+    for _ in range(args.warmup):
+        cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
+    sec = (time.perf_counter() - t0) / args.steps
+    value = t_cpu / sec
+    sample_txt = (f"{t_cpu} of {T} tokens per step, full-size fp32 weights of all {E} experts, oracle forward+backward")
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": name, "tokens_per_gpu": T, "hidden": d, "experts": E, "topk": k, "intermediate": I,
+                   "router": w["router"], "sample_tokens_per_step": t_cpu},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample_txt},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

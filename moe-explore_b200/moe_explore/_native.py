@@ -50,6 +50,34 @@ class MoeNativeError(RuntimeError):
 
 _lib = None
 
+# Instrumentation used by the benchmark: LAUNCHES counts this library's kernel launches; when
+# PROFILE is a dict, the grouped-GEMM wrappers bracket their launch with CUDA events on the
+# current stream and append (start, end) under a key naming the kernel variant.
+LAUNCHES = 0
+PROFILE = None
+
+
+def _count(n: int) -> None:
+    global LAUNCHES
+    LAUNCHES += n
+
+
+class _Timed:
+    def __init__(self, key: str):
+        self.key = key if PROFILE is not None else None
+
+    def __enter__(self):
+        if self.key is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+
+    def __exit__(self, *exc):
+        if self.key is not None:
+            self.end.record()
+            PROFILE.setdefault(self.key, []).append((self.start, self.end))
+        return False
+
 
 def load() -> ctypes.CDLL:
     """Load the shared library once; raises if it has not been built."""
@@ -122,6 +150,7 @@ def routing_metadata(expert_idx, num_experts, group_indices, perm, pad_offsets, 
                                      _ptr(mtile_expert), _ptr(num_mtiles), _ptr(status), _ptr(workspace),
                                      workspace.numel() * workspace.element_size(), _stream())
     _check("moe_routing_metadata", rc)
+    _count(3 if expert_idx.numel() > 0 else 1)
 
 
 def routing_workspace_bytes(num_rows: int, num_experts: int) -> int:
@@ -133,6 +162,7 @@ def layout_from_groups(group_indices, num_rows, num_experts, pad_offsets, row_sr
     rc = load().moe_layout_from_groups(_ptr(group_indices), num_rows, num_experts, _ptr(pad_offsets), _ptr(row_src),
                                        _ptr(dst_row), _ptr(mtile_expert), _ptr(num_mtiles), _stream())
     _check("moe_layout_from_groups", rc)
+    _count(2 if num_rows > 0 else 1)
 
 
 def gather_rows(src, row_src, num_mtiles, dst, div):
@@ -140,6 +170,7 @@ def gather_rows(src, row_src, num_mtiles, dst, div):
     rc = load().moe_gather_rows(_ptr(src), src.size(0), _ptr(row_src), _ptr(num_mtiles), _ptr(dst), dst.size(0),
                                 src.size(1), div, dtype_code(src.dtype), _stream())
     _check("moe_gather_rows", rc)
+    _count(1)
 
 
 def unpad_rows(src, dst_row, out):
@@ -147,6 +178,7 @@ def unpad_rows(src, dst_row, out):
     rc = load().moe_unpad_rows(_ptr(src), _ptr(dst_row), _ptr(out), out.size(0), out.size(1),
                                dtype_code(src.dtype), _stream())
     _check("moe_unpad_rows", rc)
+    _count(1)
 
 
 def combine_topk(ys, scores, dst_row, out, topk):
@@ -154,6 +186,7 @@ def combine_topk(ys, scores, dst_row, out, topk):
     rc = load().moe_combine_topk(_ptr(ys), _ptr(scores), _ptr(dst_row), _ptr(out), out.size(0), topk, out.size(1),
                                  dtype_code(ys.dtype), _stream())
     _check("moe_combine_topk", rc)
+    _count(1)
 
 
 def combine_bwd(dout, scores, ys, row_src, num_mtiles, gs, dscores, topk):
@@ -162,6 +195,7 @@ def combine_bwd(dout, scores, ys, row_src, num_mtiles, gs, dscores, topk):
                                 _ptr(dscores), dout.size(0), topk, gs.size(0), dout.size(1), dtype_code(dout.dtype),
                                 _stream())
     _check("moe_combine_bwd", rc)
+    _count(1)
 
 
 def mgrouped_gemm(a, w, out, pre_act, mtile_expert, num_mtiles, w_transposed, act, status=None):
@@ -169,24 +203,31 @@ def mgrouped_gemm(a, w, out, pre_act, mtile_expert, num_mtiles, w_transposed, ac
     E = w.size(0)
     K = a.size(1)
     N = w.size(1) if w_transposed else w.size(2)
-    rc = load().moe_mgrouped_gemm(_ptr(a), _ptr(w), _ptr(out), _ptr(pre_act), _ptr(mtile_expert), _ptr(num_mtiles),
-                                  a.size(0), K, N, E, 1 if w_transposed else 0, ACT_CODES[act], dtype_code(a.dtype),
-                                  _ptr(status), _stream())
+    key = "mgrouped_gemm:" + ("glu" if act in ("swiglu", "geglu") else ("wt" if w_transposed else "plain"))
+    with _Timed(key):
+        rc = load().moe_mgrouped_gemm(_ptr(a), _ptr(w), _ptr(out), _ptr(pre_act), _ptr(mtile_expert),
+                                      _ptr(num_mtiles), a.size(0), K, N, E, 1 if w_transposed else 0, ACT_CODES[act],
+                                      dtype_code(a.dtype), _ptr(status), _stream())
     _check("moe_mgrouped_gemm", rc)
+    _count(1)
 
 
 def mgrouped_gemm_dglu(g, w, pre_act, d_pre, mtile_expert, num_mtiles, act, status=None):
     require_cuda(g, w, pre_act, d_pre)
     E, N, K = w.shape
-    rc = load().moe_mgrouped_gemm_dglu(_ptr(g), _ptr(w), _ptr(pre_act), _ptr(d_pre), _ptr(mtile_expert),
-                                       _ptr(num_mtiles), g.size(0), K, N, E, ACT_CODES[act], dtype_code(g.dtype),
-                                       _ptr(status), _stream())
+    with _Timed("mgrouped_gemm:dglu"):
+        rc = load().moe_mgrouped_gemm_dglu(_ptr(g), _ptr(w), _ptr(pre_act), _ptr(d_pre), _ptr(mtile_expert),
+                                           _ptr(num_mtiles), g.size(0), K, N, E, ACT_CODES[act], dtype_code(g.dtype),
+                                           _ptr(status), _stream())
     _check("moe_mgrouped_gemm_dglu", rc)
+    _count(1)
 
 
 def kgrouped_gemm(a, b, dw, pad_offsets, status=None):
     require_cuda(a, b, dw)
     E, M, N = dw.shape
-    rc = load().moe_kgrouped_gemm(_ptr(a), _ptr(b), _ptr(dw), _ptr(pad_offsets), a.size(0), M, N, E,
-                                  dtype_code(a.dtype), _ptr(status), _stream())
+    with _Timed("kgrouped_gemm"):
+        rc = load().moe_kgrouped_gemm(_ptr(a), _ptr(b), _ptr(dw), _ptr(pad_offsets), a.size(0), M, N, E,
+                                      dtype_code(a.dtype), _ptr(status), _stream())
     _check("moe_kgrouped_gemm", rc)
+    _count(1)

@@ -1,0 +1,75 @@
+"""Host-side pieces that need no GPU: parameter bundles, the activation enum, router dispatch,
+weight interleaving, and the differentiable torch cross-check of the layer."""
+import pytest
+import torch
+
+from moe_explore.functional.activation import Activation, activation
+from moe_explore.functional.topk_moe import topk_moe_torch
+from moe_explore.params import (ErnieRouterParams, GLUParams, MLPParams, MOEParams, RouterParams, TopkRouterParams,
+                                interleave_gate_up)
+from moe_explore.router import router
+from oracle import moe_oracle as O
+
+
+def test_dataclasses_keep_the_reference_field_order():
+    w = torch.zeros(2, 4, 8)
+    mlp = MLPParams(w, w, "swiglu")
+    assert (mlp.weight1 is w) and mlp.activation == "swiglu"
+    r = TopkRouterParams(torch.zeros(4, 2), 2)
+    assert r.softmax_before_topk is True and r.normalize_routing is False
+    p = MOEParams(r, mlp, 2, 2)
+    assert p.shared_expert_params is None and p.num_experts == 2 and p.topk == 2
+    g = GLUParams(w, w, w, Activation.SWIGLU)
+    assert g.activation == "swiglu"
+
+
+def test_activation_enum_and_errors():
+    x = torch.randn(3, 8)
+    assert torch.equal(activation(x, Activation.SWIGLU), O.activation(x, "swiglu"))
+    assert torch.equal(activation(x, "geglu"), O.activation(x, "geglu"))
+    assert torch.equal(activation(x, "silu"), O.activation(x, "silu"))
+    assert torch.equal(activation(x, "gelu"), O.activation(x, "gelu"))
+    with pytest.raises(AssertionError):
+        activation(x, "relu")
+    with pytest.raises(AssertionError):
+        activation(torch.randn(3, 7), "swiglu")
+
+
+def test_router_dispatch_and_values():
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(10, 16, generator=g)
+    wr = torch.randn(16, 6, generator=g)
+    for sb in (True, False):
+        for nm in (True, False):
+            s, i = router(x, TopkRouterParams(wr, 2, sb, nm))
+            so, io = O.topk_router(x, wr, 2, sb, nm)
+            assert torch.equal(i, io) and torch.equal(s, so)
+    bias = torch.randn(6, generator=g)
+    s, i = router(x, ErnieRouterParams(wr, bias, 2))
+    so, io = O.ernie_router(x, wr, bias, 2)
+    assert torch.equal(i, io) and torch.equal(s, so)
+    with pytest.raises(ValueError, match="Unsupported router type"):
+        router(x, RouterParams())
+
+
+def test_interleave_gate_up():
+    gate = torch.arange(24.).reshape(2, 3, 4)
+    up = -gate
+    w = interleave_gate_up(gate, up)
+    assert w.shape == (2, 3, 8)
+    assert torch.equal(w[..., 0::2], gate) and torch.equal(w[..., 1::2], up)
+
+
+def test_torch_cross_check_matches_oracle_and_is_differentiable():
+    g = torch.Generator().manual_seed(1)
+    T, d, E, k, I = 32, 16, 4, 2, 8
+    x = torch.randn(T, d, generator=g, requires_grad=True)
+    wr = (torch.randn(d, E, generator=g) * 0.1).requires_grad_(True)
+    w1 = (torch.randn(E, d, 2 * I, generator=g) * 0.1).requires_grad_(True)
+    w2 = (torch.randn(E, I, d, generator=g) * 0.1).requires_grad_(True)
+    params = MOEParams(TopkRouterParams(wr, k, False, False), MLPParams(w1, w2, "swiglu"), E, k)
+    out = topk_moe_torch(x, params)
+    ref = O.topk_moe(x, wr, w1, w2, k, "swiglu", False, False)
+    torch.testing.assert_close(out, ref)
+    out.sum().backward()
+    assert all(t.grad is not None and torch.isfinite(t.grad).all() for t in (x, wr, w1, w2))
