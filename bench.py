@@ -72,7 +72,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.gpu_index), "-lms", "100"], stdout=subprocess.PIPE,
+                                          "-i", str(self.gpu_index), "-lms", "50"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -190,7 +190,9 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=device)
 
     name = args.workload or ("mixtral_8x7b" if world == 1 else "deepseek_v3_ep")
-    w = WORKLOADS[name]
+    w = dict(WORKLOADS[name])
+    if args.tokens:
+        w["T"] = args.tokens
     inp = make_inputs(w, device, rank, world)
     with_router = inp["router_weight"] is not None
     x, grad_out = inp["x"], inp["grad_out"]
@@ -259,7 +261,24 @@ def run_ours(args):
     clocks = sampler.stop() if rank == 0 else None
     status_ok = True
 
-    # ---- end to end: pinned host buffers in, results read back, every step ----
+    e2e_ms = None
+    if not args.device_only:
+        e2e_ms = run_e2e(args, step, x, grad_out, sync_all)
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms if e2e_ms is not None else 0.0], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
+
+    if rank == 0:
+        report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_e2e(args, step, x, grad_out, sync_all):
+    """End to end: pinned host buffers in, results read back, every step; returns ms per step."""
     hx = torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(x)
     hg = torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(grad_out)
     h_out = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for _ in range(2)]
@@ -308,14 +327,11 @@ def run_ours(args):
     e2e_loop(args.steps)
     t1.record()
     sync_all()
-    e2e_ms = t0.elapsed_time(t1) / args.steps
+    return t0.elapsed_time(t1) / args.steps
 
-    if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
 
-    if rank == 0:
+def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router):
+    if True:
         peaks = measured_peaks()
         tokens = w["T"] * world
         flops = algorithmic_flops(w, tokens, with_router)
@@ -330,9 +346,10 @@ def run_ours(args):
                        "l2": "inputs larger than L2 (expert weights are re-read from HBM every step)",
                        "flops_per_step": flops},
             "clocks": clocks,
-            "e2e": {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": 2 * x.numel() * x.element_size() * world,
-                    "d2h_bytes_per_step": 2 * x.numel() * x.element_size() * world},
+            "e2e": None if e2e_ms is None else {
+                "value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": 2 * x.numel() * x.element_size() * world,
+                "d2h_bytes_per_step": 2 * x.numel() * x.element_size() * world},
             "gpu_launches": launches,
         }
         # roofline of the dominant kernel: the gate/up grouped GEMM (4*R*d*I FLOPs per launch)
@@ -349,12 +366,9 @@ def run_ours(args):
                                 "frac": ach / peaks["sustained"], "peak_source": peaks["source"] + " (sustained)",
                                 "frac_of_burst_peak": ach / peaks["burst"], "avg_launch_ms": avg,
                                 "launches_timed": len(durs), "traffic": TRAFFIC_BYTES.get(name)}
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.device_only:
             line["cpu_baseline"] = cpu_baseline(w, inp, budget_s=20.0)
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 # DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu capture summarised
@@ -377,15 +391,16 @@ def cpu_step(xs, scores, idx, w1, w2, grad):
 
 def cpu_sample_inputs(w, inp, t_cpu):
     """First t_cpu tokens of the workload, same weights, upcast to fp32 on the host."""
-    x = inp["x"][:t_cpu].float().cpu().requires_grad_()
-    grad = inp["grad_out"][:t_cpu].float().cpu()
-    if inp["router_weight"] is not None:
-        logits = (inp["x"][:t_cpu] @ inp["router_weight"]).float().cpu()
-    else:
-        logits = inp["logits"][:t_cpu].float().cpu()
-    top, idx = torch.topk(logits, w["k"], dim=-1, sorted=False)
-    scores = torch.softmax(top, -1).requires_grad_()
-    return x, scores, idx, grad
+    with torch.no_grad():
+        x = inp["x"][:t_cpu].float().cpu()
+        grad = inp["grad_out"][:t_cpu].float().cpu()
+        if inp["router_weight"] is not None:
+            logits = (inp["x"][:t_cpu] @ inp["router_weight"]).float().cpu()
+        else:
+            logits = inp["logits"][:t_cpu].float().cpu()
+        top, idx = torch.topk(logits, w["k"], dim=-1, sorted=False)
+        scores = torch.softmax(top, -1)
+    return x.requires_grad_(), scores.requires_grad_(), idx, grad
 
 
 def cpu_baseline(w, inp, budget_s):
@@ -479,6 +494,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")
+    ap.add_argument("--device-only", action="store_true",
+                    help="skip the end-to-end and CPU-baseline legs (for short runs under a profiler)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
