@@ -92,6 +92,21 @@ int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows, int num_ex
                          int32_t* num_mtiles, int32_t* status, void* workspace,
                          size_t workspace_bytes, void* stream);
 
+/* The same computation for callers that cannot allocate device memory (fixed arenas, plugin
+ * hosts that hand an operator only its inputs and outputs, loops that must stay off the
+ * allocator): the scratch is a 1 MiB array built into the library image, present on every GPU
+ * that loads it.  Inputs and outputs are still the caller's.  It has no counterpart in the
+ * reference.  Limits: moe_routing_workspace_bytes(num_rows, num_experts) must not exceed
+ * moe_routing_static_scratch_bytes() (e.g. 524288 rows x 256 experts fits exactly), otherwise
+ * MOE_ERR_UNSUPPORTED.  All calls on one device share the array, so calls that overlap on the
+ * GPU race; the array needs no clearing between calls.  The first call on each device resolves
+ * the array's device address and should be made outside stream capture. */
+size_t moe_routing_static_scratch_bytes(void);
+int moe_routing_metadata_static(const int64_t* expert_idx, int64_t num_rows, int num_experts,
+                                int32_t* group_indices, int64_t* perm, int32_t* pad_offsets,
+                                int32_t* row_src, int32_t* dst_row, int32_t* mtile_expert,
+                                int32_t* num_mtiles, int32_t* status, void* stream);
+
 /* Same outputs from an existing exclusive prefix `group_indices` [E+1] (rows already in
  * expert order, identity permutation): used by the plain ragged grouped GEMM
  * (m_grouped_gemm with gather=scatter=False, triton_kernels/m_grouped_gemm.py:332-393).

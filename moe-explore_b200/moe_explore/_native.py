@@ -29,6 +29,8 @@ SIGNATURES = {
     "moe_mtiles_bound": (c_int64, [c_int64, c_int]),
     "moe_routing_workspace_bytes": (c_size_t, [c_int64, c_int]),
     "moe_routing_metadata": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 8 + [c_void_p, c_size_t, c_void_p]),
+    "moe_routing_static_scratch_bytes": (c_size_t, []),
+    "moe_routing_metadata_static": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 8 + [c_void_p]),
     "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 5 + [c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
@@ -150,6 +152,18 @@ def routing_metadata(expert_idx, num_experts, group_indices, perm, pad_offsets, 
                                      _ptr(mtile_expert), _ptr(num_mtiles), _ptr(status), _ptr(workspace),
                                      workspace.numel() * workspace.element_size(), _stream())
     _check("moe_routing_metadata", rc)
+    _count(3 if expert_idx.numel() > 0 else 1)
+
+
+def routing_metadata_static(expert_idx, num_experts, group_indices, perm, pad_offsets, row_src, dst_row, mtile_expert,
+                            num_mtiles, status):
+    """Routing metadata with the library's built-in scratch: for callers that cannot allocate
+    device memory.  Calls on one device must not overlap; see include/moe_sm100.h for the limits."""
+    require_cuda(expert_idx)
+    rc = load().moe_routing_metadata_static(_ptr(expert_idx), expert_idx.numel(), num_experts, _ptr(group_indices),
+                                            _ptr(perm), _ptr(pad_offsets), _ptr(row_src), _ptr(dst_row),
+                                            _ptr(mtile_expert), _ptr(num_mtiles), _ptr(status), _stream())
+    _check("moe_routing_metadata_static", rc)
     _count(3 if expert_idx.numel() > 0 else 1)
 
 
