@@ -356,16 +356,19 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
         dom = profile.get("mgrouped_gemm:glu") if profile else None
         if dom:
             torch.cuda.synchronize()
-            durs = [a.elapsed_time(b) for a, b in dom]
+            durs = [a.elapsed_time(b) for a, b, _ in dom]
             avg = sum(durs) / len(durs)
-            rows_local = w["T"] * w["k"]  # mean routed rows per GPU
+            rows_local = sum(r for _, _, r in dom) / len(dom)  # routed rows this rank's launches handled
             kflops = 4.0 * rows_local * w["d"] * w["I"]
             ach = kflops / (avg * 1e-3) / 1e12
             line["roofline"] = {"kernel": "grouped_gemm_kernel<gate/up, SwiGLU epilogue>", "bound": "tensor",
                                 "achieved": ach, "peak": peaks["sustained"], "unit": "TFLOP/s",
                                 "frac": ach / peaks["sustained"], "peak_source": peaks["source"] + " (sustained)",
                                 "frac_of_burst_peak": ach / peaks["burst"], "avg_launch_ms": avg,
-                                "launches_timed": len(durs), "traffic": TRAFFIC_BYTES.get(name)}
+                                "launches_timed": len(durs), "rows_per_launch": rows_local, "traffic": TRAFFIC_BYTES.get(name)}
+        if profile:
+            line["section_ms_per_step"] = {k_: round(sum(a.elapsed_time(b) for a, b, _ in v) / args.steps, 4)
+                                           for k_, v in sorted(profile.items())}
         if world == 1 and not args.no_cpu_baseline and not args.device_only:
             line["cpu_baseline"] = cpu_baseline(w, inp, budget_s=20.0)
         print(json.dumps(line), flush=True)

@@ -80,8 +80,12 @@ int64_t moe_mtiles_bound(int64_t num_rows, int num_experts);
  *   row_src       int32 [RP]     flat position held by padded row p, or -1 for padding
  *   dst_row       int32 [R]      padded row that holds flat position j (inverse of row_src)
  *   mtile_expert  int32 [moe_mtiles_bound]  expert of each 128-row tile
- *   num_mtiles    int32 [1]      number of 128-row tiles in use
- * Any of perm / row_src / dst_row / mtile_expert+num_mtiles may be NULL to skip it.
+ *   tile_pairs    int32 [moe_mtiles_bound]  row tiles grouped in pairs of the same expert (two
+ *                                row tiles share one weight tile on a pair of SMs): entry p = first
+ *                                tile (bits 0-19) | expert (bits 20-30) | bit 31 when tile+1 is in
+ *                                the pair too
+ *   num_mtiles    int32 [2]      {number of 128-row tiles in use, number of tile pairs}
+ * Any of perm / row_src / dst_row / (mtile_expert, tile_pairs, num_mtiles) may be NULL to skip it.
  * ids outside [0, E) are rejected on the device: they are dropped from every output and
  * `status` is set.  Workspace: moe_routing_workspace_bytes(R, E) bytes.
  * --------------------------------------------------------------------------------- */
@@ -89,8 +93,8 @@ size_t moe_routing_workspace_bytes(int64_t num_rows, int num_experts);
 int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows, int num_experts,
                          int32_t* group_indices, int64_t* perm, int32_t* pad_offsets,
                          int32_t* row_src, int32_t* dst_row, int32_t* mtile_expert,
-                         int32_t* num_mtiles, int32_t* status, void* workspace,
-                         size_t workspace_bytes, void* stream);
+                         int32_t* tile_pairs, int32_t* num_mtiles, int32_t* status,
+                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* The same computation for callers that cannot allocate device memory (fixed arenas, plugin
  * hosts that hand an operator only its inputs and outputs, loops that must stay off the
@@ -105,7 +109,8 @@ size_t moe_routing_static_scratch_bytes(void);
 int moe_routing_metadata_static(const int64_t* expert_idx, int64_t num_rows, int num_experts,
                                 int32_t* group_indices, int64_t* perm, int32_t* pad_offsets,
                                 int32_t* row_src, int32_t* dst_row, int32_t* mtile_expert,
-                                int32_t* num_mtiles, int32_t* status, void* stream);
+                                int32_t* tile_pairs, int32_t* num_mtiles, int32_t* status,
+                                void* stream);
 
 /* Same outputs from an existing exclusive prefix `group_indices` [E+1] (rows already in
  * expert order, identity permutation): used by the plain ragged grouped GEMM
@@ -113,7 +118,8 @@ int moe_routing_metadata_static(const int64_t* expert_idx, int64_t num_rows, int
  * row_src[p] is the unpadded row index. */
 int moe_layout_from_groups(const int32_t* group_indices, int64_t num_rows, int num_experts,
                            int32_t* pad_offsets, int32_t* row_src, int32_t* dst_row,
-                           int32_t* mtile_expert, int32_t* num_mtiles, void* stream);
+                           int32_t* mtile_expert, int32_t* tile_pairs, int32_t* num_mtiles,
+                           void* stream);
 
 /* ---------------------------------------------------------------------------------
  * Row movement (HBM-bound).  Replace row_gather / row_scatter
@@ -154,12 +160,15 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  * --------------------------------------------------------------------------------- */
 
 /* M-grouped: out = epilogue(a[rows of tile] @ w[expert of tile]).
+ *   mtile_expert / tile_pairs / num_mtiles come from moe_routing_metadata; tile_pairs may be
+ *   NULL, which selects the one-SM-per-tile kernels instead of the paired-SM ones.
  *   a    [RP, K]
  *   w    [E, K, N] when w_transposed == 0, [E, N, K] when w_transposed == 1
  *   act  MOE_ACT_NONE/SILU/GELU: out [RP, N];  MOE_ACT_SWIGLU/GEGLU: out [RP, N/2] and,
  *        when pre_act != NULL, pre_act [RP, N] receives the un-activated product. */
 int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act,
-                      const int32_t* mtile_expert, const int32_t* num_mtiles,
+                      const int32_t* mtile_expert, const int32_t* tile_pairs,
+                      const int32_t* num_mtiles,
                       int64_t padded_rows, int K, int N, int num_experts, int w_transposed,
                       int act, int dtype, int32_t* status, void* stream);
 
@@ -168,7 +177,8 @@ int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act,
  * pre_act = the saved gate/up product.  act must be MOE_ACT_SWIGLU or MOE_ACT_GEGLU.
  * No counterpart in the reference (it has no backward). */
 int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, void* d_pre,
-                           const int32_t* mtile_expert, const int32_t* num_mtiles,
+                           const int32_t* mtile_expert, const int32_t* tile_pairs,
+                           const int32_t* num_mtiles,
                            int64_t padded_rows, int K, int N, int num_experts, int act,
                            int dtype, int32_t* status, void* stream);
 

@@ -10,26 +10,39 @@
 //   K-grouped (contraction over an expert's rows, one output matrix per expert):
 //     dW1[e] = Xs_e^T @ dH_e, dW2[e] = Act_e^T @ Gs_e      A and B both MN-major
 //
-// Roles inside a CTA (192 threads, one CTA per SM):
+// Roles inside a CTA (320 threads, one CTA per SM):
 //   warp 0      : TMA producer  -- one lane issues cp.async.bulk.tensor tile loads into a
 //                 ring of shared-memory stages (128-byte swizzle), signalled by mbarriers;
 //   warp 1      : MMA issuer    -- one lane issues tcgen05.mma (128 x BN x 16, fp32
 //                 accumulators in TMEM, two accumulator stages) and tcgen05.commit;
-//   warps 2..5  : epilogue      -- tcgen05.ld the accumulator (each warp its 32-lane
-//                 quadrant), apply the fused epilogue, store 16-byte vectors to global.
+//   warps 2..9  : epilogue      -- tcgen05.ld the accumulator (each warp its 32-lane
+//                 quadrant and half of the columns), apply the fused epilogue, store 16-byte
+//                 vectors to global.
 // The accumulator of tile i+1 is produced while tile i is being drained.
+//
+// CTA pairs (template parameter CTAS = 2, launched as clusters of two): the two CTAs of a pair work
+// on two row tiles of the same expert against the same weight tile.  Each CTA loads its own 128 A
+// rows and HALF of the B columns; one tcgen05.mma.cta_group::2 issued by the pair's leader spans
+// both SMs (256 x BN accumulator, 128 rows in each CTA's TMEM) and reads the B halves from both
+// CTAs' shared memory.  That halves the B bytes each SM pulls from L2 and reads from shared memory
+// per FLOP.  Every CTA fetches its own tiles with its own loads; nothing is broadcast.  Operand
+// arrival is credited to the leader's mbarriers, stage release and accumulator-ready signals go to
+// both CTAs (two tcgen05.commit), accumulator-drained arrivals come back to the leader.
 //
 // Replaces the Triton kernels m_grouped_gemm_persistent_kernel / m_grouped_gemm_inner_kernel
 // (reference: src/moe_explore/triton_kernels/m_grouped_gemm.py:33-267) and their epilogues
 // (epilogue_split.py:4-44, triton_kernels/activation.py:5-36).
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace moe {
 
-constexpr int BM = 128;       // accumulator rows  (= TMEM lanes)
+constexpr int BM = 128;       // accumulator rows per CTA (= TMEM lanes)
 constexpr int BK = 64;        // K extent of one shared-memory stage: 64 x 2 bytes = one 128-byte swizzle row
 constexpr int UMMA_K = 16;    // K extent of one tcgen05.mma for 16-bit inputs
-constexpr int kThreads = 192;
+constexpr int kEpilogueWarps = 8;
+constexpr int kThreads = 64 + 32 * kEpilogueWarps;
 constexpr int kGroupM = 16;   // consecutive row tiles that share a sweep over column tiles (L2 reuse)
 constexpr uint32_t kTmemCols = 512;
 
@@ -38,7 +51,8 @@ enum Epilogue : int { EPI_ACT = 0, EPI_GLU = 1, EPI_DGLU = 2 };
 struct GemmArgs {
   // scheduling
   const int32_t* mtile_expert;  // M-grouped: expert of each 128-row tile
-  const int32_t* num_mtiles;    // M-grouped: device scalar, tiles in use
+  const int32_t* tile_pairs;    // M-grouped, CTA pairs: first tile of each pair, bit 31 = the pair has a second tile
+  const int32_t* num_mtiles;    // M-grouped: device int32[2] = {tiles in use, tile pairs in use}
   const int32_t* pad_offsets;   // K-grouped: padded row offsets [E+1]
   int32_t num_experts;
   int32_t m_dim;  // K-grouped: rows of each output matrix
@@ -53,11 +67,12 @@ struct GemmArgs {
 };
 
 struct TileCoord {
-  int m0;      // first accumulator row: padded row (M-grouped) or output-matrix row (K-grouped)
-  int n0;      // first accumulator column
+  int m0;       // first accumulator row of THIS CTA: padded row (M-grouped) or output-matrix row (K-grouped)
+  int n0;       // first accumulator column of the tile
   int expert;
-  int k_row0;  // K-grouped: first padded row of the contraction
-  int kiters;  // number of BK-deep stages to contract
+  int k_row0;   // K-grouped: first padded row of the contraction
+  int kiters;   // number of BK-deep stages to contract
+  bool active;  // false for the second CTA of a pair whose expert has an odd number of row tiles
 };
 
 // ----------------------------------------------------------------------------------
@@ -85,7 +100,8 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr, uint32_t lbo_b
 }
 
 // Instruction descriptor (32-bit): fp32 accumulate, 16-bit A/B format, operand majorness, N>>3, M>>4.
-template <typename T, int BN, bool A_K, bool B_K>
+// With a CTA pair the instruction covers M = 256 rows (128 per CTA).
+template <typename T, int BN, bool A_K, bool B_K, int CTAS>
 __device__ __forceinline__ constexpr uint32_t make_idesc() {
   uint32_t d = 0;
   d |= 1u << 4;                       // D format: F32
@@ -94,35 +110,38 @@ __device__ __forceinline__ constexpr uint32_t make_idesc() {
   d |= (A_K ? 0u : 1u) << 15;         // A major: 0 = K, 1 = MN
   d |= (B_K ? 0u : 1u) << 16;         // B major
   d |= static_cast<uint32_t>(BN >> 3) << 17;
-  d |= static_cast<uint32_t>(BM >> 4) << 24;
+  d |= static_cast<uint32_t>((BM * CTAS) >> 4) << 24;
   return d;
 }
 
-template <int BN>
+template <int BN, int CTAS>
 struct SmemPlan {
   static constexpr int kABytes = BM * BK * 2;
-  static constexpr int kBBytes = BN * BK * 2;
+  static constexpr int kBCols = BN / CTAS;        // B columns held by one CTA
+  static constexpr int kBBytes = kBCols * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <bool KG>
+// Number of (row unit, column tile) work items and the row-unit / column-tile counts.  A row unit is
+// one 128-row tile (one CTA) or a pair of them (CTA pair).
+template <bool KG, int CTAS>
 __device__ __forceinline__ int total_tiles(const GemmArgs& args, int& mt, int& nt, int BN) {
   nt = (args.n_dim + BN - 1) / BN;
   if (KG) {
-    mt = (args.m_dim + BM - 1) / BM;
+    mt = (args.m_dim + BM * CTAS - 1) / (BM * CTAS);
     return args.num_experts * mt * nt;
   }
-  mt = *args.num_mtiles;
+  mt = args.num_mtiles[CTAS - 1];
   return mt * nt;
 }
 
-// Row tiles are walked in groups of kGroupM: inside a group every column tile is visited for
-// all rows of the group before moving on, so concurrently running CTAs share operand tiles in L2.
-template <bool KG>
-__device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const GemmArgs& args, int BN) {
+// Row units are walked in groups of kGroupM: inside a group every column tile is visited for all
+// rows of the group before moving on, so concurrently running CTAs share operand tiles in L2.
+template <bool KG, int CTAS>
+__device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const GemmArgs& args, int BN, int rank) {
   TileCoord c;
   int expert = 0;
   if (KG) {
@@ -136,14 +155,27 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const Ge
   const int gm = min(kGroupM, mt - m_first);
   const int n_idx = rem / gm;
   const int m_idx = m_first + (rem - n_idx * gm);
-  c.m0 = m_idx * BM;
   c.n0 = n_idx * BN;
+  c.active = true;
   if (KG) {
+    c.m0 = (m_idx * CTAS + rank) * BM;
     c.expert = expert;
-    c.k_row0 = args.pad_offsets[expert];
-    c.kiters = (args.pad_offsets[expert + 1] - c.k_row0) / BK;  // padded ranges are multiples of 128
+    c.k_row0 = __ldg(args.pad_offsets + expert);
+    c.kiters = (__ldg(args.pad_offsets + expert + 1) - c.k_row0) / BK;  // padded ranges are multiples of 128
   } else {
-    c.expert = args.mtile_expert[m_idx];
+    int tile = m_idx;
+    if (CTAS == 2) {
+      // one load: first tile (bits 0-19), expert (bits 20-30), "has a second tile" (bit 31)
+      const uint32_t info = static_cast<uint32_t>(__ldg(args.tile_pairs + m_idx));
+      const bool second = (info >> 31) != 0;
+      tile = static_cast<int>(info & 0xFFFFFu);
+      c.expert = static_cast<int>((info >> 20) & 0x7FFu);
+      c.active = rank == 0 || second;
+      if (rank == 1 && second) tile += 1;  // an inactive second CTA re-reads the first tile and stores nothing
+    } else {
+      c.expert = __ldg(args.mtile_expert + tile);
+    }
+    c.m0 = tile * BM;
     c.k_row0 = 0;
     c.kiters = (args.k_dim + BK - 1) / BK;
   }
@@ -161,35 +193,39 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
   return r;
 }
 
-template <typename T, int BN, bool A_K, bool B_K, int EPI, bool KG>
+template <typename T, int BN, bool A_K, bool B_K, int EPI, bool KG, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const GemmArgs args) {
-  using Plan = SmemPlan<BN>;
+  using Plan = SmemPlan<BN, CTAS>;
   constexpr int kStages = Plan::kStages;
+  constexpr bool kPair = CTAS == 2;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;  // 128-byte swizzle atoms need 1024-byte alignment
   uint8_t* tiles = smem_raw + (tiles_addr - raw_addr);
   uint64_t* bars = reinterpret_cast<uint64_t*>(tiles + kStages * Plan::kStageBytes);
-  const uint32_t full_bar = smem_u32(bars);                     // [kStages]
-  const uint32_t empty_bar = smem_u32(bars + kStages);          // [kStages]
-  const uint32_t tfull_bar = smem_u32(bars + 2 * kStages);      // [2]
-  const uint32_t tempty_bar = smem_u32(bars + 2 * kStages + 2); // [2]
+  const uint32_t full_bar = smem_u32(bars);                     // [kStages]  (used in the leader CTA)
+  const uint32_t empty_bar = smem_u32(bars + kStages);          // [kStages]  (one set per CTA)
+  const uint32_t tfull_bar = smem_u32(bars + 2 * kStages);      // [2]        (one set per CTA)
+  const uint32_t tempty_bar = smem_u32(bars + 2 * kStages + 2); // [2]        (used in the leader CTA)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  const int rank = kPair ? static_cast<int>(cluster_ctarank()) : 0;  // 0 = leader of the pair
+  const int unit = blockIdx.x / CTAS;        // persistent worker index (CTA or CTA pair)
+  const int num_units = gridDim.x / CTAS;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(full_bar + 8 * s, 1);
+      mbar_init(full_bar + 8 * s, CTAS);   // one arrive.expect_tx per CTA
       mbar_init(empty_bar + 8 * s, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(tfull_bar + 8 * a, 1);
-      mbar_init(tempty_bar + 8 * a, 128);
+      mbar_init(tempty_bar + 8 * a, kEpilogueWarps * CTAS);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -197,16 +233,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     tma_prefetch_desc(&tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();  // the peer's barriers must be initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   int mt, nt;
-  const int ntiles = total_tiles<KG>(args, mt, nt, BN);
+  const int ntiles = total_tiles<KG, CTAS>(args, mt, nt, BN);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -214,31 +256,60 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-        const TileCoord c = decode_tile<KG>(t, mt, nt, args, BN);
+      const int bcol = rank * Plan::kBCols;  // this CTA's share of the tile's B columns
+      TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, args, BN, rank);
+      for (int t = unit; t < ntiles && ok; t += num_units) {
+        const TileCoord c = c_next;
+        // fetch the next work item's coordinates now; the loads complete while this tile streams
+        if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, args, BN, rank);
         for (int kb = 0; kb < c.kiters; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, args.status, DS_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
           }
-          const uint32_t fb = full_bar + 8 * stage;
           const uint32_t sa = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t sb = sa + Plan::kABytes;
-          mbar_arrive_expect_tx(fb, Plan::kStageBytes);
-          if (KG) {
-            const int krow = c.k_row0 + kb * BK;
+          if (kPair && rank != 0) {
+            // the second CTA credits the LEADER's barrier: the leader issues the MMA that reads both halves
+            const uint32_t fb = mapa_shared(full_bar + 8 * stage, 0);
+            mbar_arrive_expect_tx_cluster(fb, Plan::kStageBytes);
+            if (KG) {
+              const int krow = c.k_row0 + kb * BK;
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmap_a, c.m0 + 64 * j, krow, fb);
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmap_a, c.m0 + 64 * j, krow, fb);
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), &tmap_b, c.n0 + 64 * j, krow, fb);
-          } else {
-            tma_load_2d(sa, &tmap_a, kb * BK, c.m0, fb);
-            if (B_K) {
-              tma_load_3d(sb, &tmap_b, kb * BK, c.n0, c.expert, fb);
+              for (int j = 0; j < Plan::kBCols / 64; ++j)
+                tma_load_2d_pair(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, krow, fb);
             } else {
+              tma_load_2d_pair(sa, &tmap_a, kb * BK, c.m0, fb);
+              if (B_K) {
+                tma_load_3d_pair(sb, &tmap_b, kb * BK, c.n0 + bcol, c.expert, fb);
+              } else {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j)
-                tma_load_3d(sb + j * (BK * 128), &tmap_b, c.n0 + 64 * j, kb * BK, c.expert, fb);
+                for (int j = 0; j < Plan::kBCols / 64; ++j)
+                  tma_load_3d_pair(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, kb * BK, c.expert, fb);
+              }
+            }
+          } else {
+            // single CTA, or the leader of a pair: everything is local
+            const uint32_t fb = full_bar + 8 * stage;
+            mbar_arrive_expect_tx(fb, Plan::kStageBytes);
+            if (KG) {
+              const int krow = c.k_row0 + kb * BK;
+#pragma unroll
+              for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmap_a, c.m0 + 64 * j, krow, fb);
+#pragma unroll
+              for (int j = 0; j < Plan::kBCols / 64; ++j)
+                tma_load_2d(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, krow, fb);
+            } else {
+              tma_load_2d(sa, &tmap_a, kb * BK, c.m0, fb);
+              if (B_K) {
+                tma_load_3d(sb, &tmap_b, kb * BK, c.n0 + bcol, c.expert, fb);
+              } else {
+#pragma unroll
+                for (int j = 0; j < Plan::kBCols / 64; ++j)
+                  tma_load_3d(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, kb * BK, c.expert, fb);
+              }
             }
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -250,16 +321,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer --------------------------------
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc<T, BN, A_K, B_K>();
+    // ------------------------------ MMA issuer (leader CTA only) --------------
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc<T, BN, A_K, B_K, CTAS>();
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x) {
-        const TileCoord c = decode_tile<KG>(t, mt, nt, args, BN);
+      TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, args, BN, rank);
+      for (int t = unit; t < ntiles && ok; t += num_units) {
+        const TileCoord c = c_next;
+        if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, args, BN, rank);
         if (c.kiters == 0) continue;  // empty expert: the epilogue writes zeros on its own
         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, args.status, DS_TIMEOUT_MMA)) break;
         tc_fence_after();
@@ -280,13 +353,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                     : make_desc(sa + k * (UMMA_K * 128), BK * 128, 1024);
             const uint64_t db = B_K ? make_desc(sb + k * (UMMA_K * 2), 16, 1024)
                                     : make_desc(sb + k * (UMMA_K * 128), BK * 128, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (kPair) umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            else umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(empty_bar + 8 * stage);  // frees the stage once these MMAs have read it
+          // free the stage in every CTA whose shared memory these MMAs read
+          if (kPair) {
+            umma_commit_pair(empty_bar + 8 * stage);
+            umma_commit_pair(mapa_shared(empty_bar + 8 * stage, 1));
+          } else {
+            umma_commit(empty_bar + 8 * stage);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
-        umma_commit(tfull_bar + 8 * acc);  // accumulator complete
+        // accumulator complete: tell the epilogue warps of every CTA holding a part of it
+        if (kPair) {
+          umma_commit_pair(tfull_bar + 8 * acc);
+          umma_commit_pair(mapa_shared(tfull_bar + 8 * acc, 1));
+        } else {
+          umma_commit(tfull_bar + 8 * acc);
+        }
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok || *abort_flag) {
@@ -295,7 +381,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
-    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    // Warp w reads TMEM lane quadrant (w % 4); the two warps of a quadrant split the columns.
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kChunksPerWarp = BN / 32 / 2;
+    const int chunk_begin = half * kChunksPerWarp;
     const int row_in_tile = quad * 32 + lane;
     int acc = 0;
     uint32_t acc_phase = 0;
@@ -303,26 +393,55 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     T* aux_out = reinterpret_cast<T*>(args.aux_out);
     const T* aux_in = reinterpret_cast<const T*>(args.aux_in);
     const int N = args.n_dim;
-    for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-      const TileCoord c = decode_tile<KG>(t, mt, nt, args, BN);
+    const uint32_t tempty_leader = kPair ? mapa_shared(tempty_bar, 0) : tempty_bar;
+    TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, args, BN, rank);
+    for (int t = unit; t < ntiles; t += num_units) {
+      const TileCoord c = c_next;
+      if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, args, BN, rank);
       const bool have_acc = c.kiters != 0;
-      if (have_acc) {
-        if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, args.status, DS_TIMEOUT_EPILOGUE)) break;
-        tc_fence_after();
-      }
       const int row = c.m0 + row_in_tile;
-      bool row_ok = true;
+      bool row_ok = c.active;
       long long out_row;  // row index into the output matrix
       if (KG) {
-        row_ok = row < args.m_dim;
+        row_ok = row_ok && row < args.m_dim;
         out_row = static_cast<long long>(c.expert) * args.m_dim + row;
       } else {
         out_row = row;
       }
+      // EPI_DGLU: the saved pre-activation does not depend on the accumulator -- fetch the first
+      // chunk's 128 bytes before waiting for the MMAs, then stay one chunk ahead.
+      uint4 h_next[8];
+      const long long ld2 = 2ll * N;
+      if (EPI == EPI_DGLU) {
+        const int col0 = c.n0 + chunk_begin * 32;
+        const T* src = aux_in + out_row * ld2 + 2 * col0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          h_next[q] = (row_ok && col0 + q * 4 < N) ? __ldg(reinterpret_cast<const uint4*>(src + q * 8))
+                                                   : make_uint4(0, 0, 0, 0);
+      }
+      if (have_acc) {
+        if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, args.status, DS_TIMEOUT_EPILOGUE)) break;
+        tc_fence_after();
+      }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
 #pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+      for (int chunk = chunk_begin; chunk < chunk_begin + kChunksPerWarp; ++chunk) {
         float v[32];
+        uint4 h_cur[8];
+        const int col0 = c.n0 + chunk * 32;
+        if (EPI == EPI_DGLU) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) h_cur[q] = h_next[q];
+          if (chunk + 1 < chunk_begin + kChunksPerWarp) {
+            const int ncol0 = col0 + 32;
+            const T* src = aux_in + out_row * ld2 + 2 * ncol0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              h_next[q] = (row_ok && ncol0 + q * 4 < N) ? __ldg(reinterpret_cast<const uint4*>(src + q * 8))
+                                                        : make_uint4(0, 0, 0, 0);
+          }
+        }
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the masked stores below
         if (have_acc) {
           uint32_t raw[32];
@@ -334,7 +453,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.0f;
         }
-        const int col0 = c.n0 + chunk * 32;
         if (!row_ok || col0 >= N) {
           // nothing to store for this lane / column chunk
         } else if (EPI == EPI_ACT) {
@@ -370,14 +488,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           for (int q = 0; q < 2; ++q)
             if ((col0 >> 1) + q * 8 < half_n) *reinterpret_cast<uint4*>(dst + q * 8) = pack8<T>(g + q * 8);
         } else {  // EPI_DGLU: v = d(activated)[row, col0..col0+32); pre-activation pairs at columns 2*col
-          const long long ld2 = 2ll * N;
-          const T* src = aux_in + out_row * ld2 + 2 * col0;
           T* dst = out + out_row * ld2 + 2 * col0;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // 8 pre-activation elements = 4 (gate, up) pairs per 16 bytes
             if (col0 + q * 4 >= N) continue;
-            const uint4 h = *reinterpret_cast<const uint4*>(src + q * 8);
-            const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
+            const uint32_t hw[4] = {h_cur[q].x, h_cur[q].y, h_cur[q].z, h_cur[q].w};
             float o[8];
 #pragma unroll
             for (int p = 0; p < 4; ++p) {
@@ -400,8 +515,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
       if (have_acc) {
+        // this warp has read its part of the accumulator: one arrival per warp on the leader's barrier
         tc_fence_before();
-        mbar_arrive(tempty_bar + 8 * acc);
+        __syncwarp();
+        if (lane == 0) {
+          if (kPair && rank != 0) mbar_arrive_cluster(tempty_leader + 8 * acc);
+          else mbar_arrive(tempty_bar + 8 * acc);
+        }
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
@@ -409,10 +529,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();  // neither CTA may exit while its peer can still touch its memory or barriers
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    if (kPair) tmem_dealloc_pair(tmem_base, kTmemCols);
+    else tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -467,27 +589,68 @@ static int make_tmap(CUtensorMap* map, int dtype, const void* ptr, int rank, con
   return MOE_OK;
 }
 
-template <typename T, int BN, bool A_K, bool B_K, int EPI, bool KG>
-static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, int grid, cudaStream_t stream) {
-  auto kernel = grouped_gemm_kernel<T, BN, A_K, B_K, EPI, KG>;
-  constexpr int smem = SmemPlan<BN>::kTotal;
-  static bool configured[16] = {};
+template <typename T, int BN, bool A_K, bool B_K, int EPI, bool KG, int CTAS>
+static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t stream) {
+  auto kernel = grouped_gemm_kernel<T, BN, A_K, B_K, EPI, KG, CTAS>;
+  constexpr int smem = SmemPlan<BN, CTAS>::kTotal;
+  static int grid_for_device[16] = {};  // 0 = not configured yet
   int dev = 0;
   MOE_CUDA(cudaGetDevice(&dev));
-  if (dev < 16 && !configured[dev]) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = CTAS > 1 ? 1 : 0;
+  int grid = dev < 16 ? grid_for_device[dev] : 0;
+  if (grid == 0) {
     MOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    configured[dev] = true;
-  } else if (dev >= 16) {
-    MOE_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    grid = sm_count() / CTAS * CTAS;
+    if (CTAS > 1) {
+      // The tile loop is statically strided over the resident workers, so launch exactly as many
+      // CTA pairs as can be resident at once (a GPC with an odd SM count cannot host a last pair).
+      cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+      int clusters = 0;
+      MOE_CUDA(cudaOccupancyMaxActiveClusters(&clusters, kernel, &cfg));
+      if (clusters <= 0) {
+        set_error("grouped GEMM: no CTA pair of this kernel fits on the device");
+        return MOE_ERR_UNSUPPORTED;
+      }
+      if (clusters * CTAS < grid) grid = clusters * CTAS;
+    }
+    if (const char* g = getenv("MOE_SM100_GRID")) {  // measurement aid: cap the number of resident workers
+      const int want = atoi(g) / CTAS * CTAS;
+      if (want > 0 && want < grid) grid = want;
+    }
+    if (dev < 16) grid_for_device[dev] = grid;
+    if (getenv("MOE_SM100_DEBUG") != nullptr)
+      fprintf(stderr, "[moe_sm100] grouped GEMM BN=%d CTAS=%d KG=%d: grid %d CTAs, %d bytes of shared memory\n", BN, CTAS,
+              (int)KG, grid, smem);
   }
-  kernel<<<grid, kThreads, smem, stream>>>(ta, tb, args);
-  MOE_CUDA(cudaGetLastError());
+  cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
+  MOE_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
   return MOE_OK;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-template <typename T, int BN>
+// CTA pairs are the default; MOE_SM100_SINGLE_CTA=1 in the environment selects the one-CTA kernels
+// (kept for comparison measurements).
+static bool use_cta_pairs() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* v = getenv("MOE_SM100_SINGLE_CTA");
+    cached = (v != nullptr && v[0] == '1') ? 0 : 1;
+  }
+  return cached == 1;
+}
+
+template <typename T, int BN, int CTAS>
 static int mgrouped_dispatch(const void* a, const void* w, int64_t padded_rows, int K, int N, int E, int w_transposed,
                              int epi, const GemmArgs& args, int dtype, cudaStream_t stream) {
   CUtensorMap ta, tb;
@@ -499,7 +662,7 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t padded_rows, 
   }
   if (w_transposed) {
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)E};
-    const uint32_t box[3] = {BK, (uint32_t)BN, 1};
+    const uint32_t box[3] = {BK, (uint32_t)(BN / CTAS), 1};
     int rc = make_tmap(&tb, dtype, w, 3, dims, box);
     if (rc != MOE_OK) return rc;
   } else {
@@ -508,23 +671,23 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t padded_rows, 
     int rc = make_tmap(&tb, dtype, w, 3, dims, box);
     if (rc != MOE_OK) return rc;
   }
-  const int grid = sm_count();
   if (epi == EPI_ACT) {
-    return w_transposed ? launch<T, BN, true, true, EPI_ACT, false>(ta, tb, args, grid, stream)
-                        : launch<T, BN, true, false, EPI_ACT, false>(ta, tb, args, grid, stream);
+    return w_transposed ? launch<T, BN, true, true, EPI_ACT, false, CTAS>(ta, tb, args, stream)
+                        : launch<T, BN, true, false, EPI_ACT, false, CTAS>(ta, tb, args, stream);
   } else if (epi == EPI_GLU) {
-    return w_transposed ? launch<T, BN, true, true, EPI_GLU, false>(ta, tb, args, grid, stream)
-                        : launch<T, BN, true, false, EPI_GLU, false>(ta, tb, args, grid, stream);
+    return w_transposed ? launch<T, BN, true, true, EPI_GLU, false, CTAS>(ta, tb, args, stream)
+                        : launch<T, BN, true, false, EPI_GLU, false, CTAS>(ta, tb, args, stream);
   }
   // EPI_DGLU is only used with the transposed weight (dAct = g @ W2^T).
-  return launch<T, BN, true, true, EPI_DGLU, false>(ta, tb, args, grid, stream);
+  return launch<T, BN, true, true, EPI_DGLU, false, CTAS>(ta, tb, args, stream);
 }
 
 static int pick_bn(int N) { return (N % 256 == 0 || N % 128 != 0) ? 256 : 128; }
 
 static int mgrouped_common(const void* a, const void* w, void* out, void* aux_out, const void* aux_in,
-                           const int32_t* mtile_expert, const int32_t* num_mtiles, int64_t padded_rows, int K, int N,
-                           int E, int w_transposed, int epi, int act, int dtype, int32_t* status, void* stream) {
+                           const int32_t* mtile_expert, const int32_t* tile_pairs, const int32_t* num_mtiles,
+                           int64_t padded_rows, int K, int N, int E, int w_transposed, int epi, int act, int dtype,
+                           int32_t* status, void* stream) {
   MOE_CHECK_ARG(a && w && out && mtile_expert && num_mtiles, "grouped GEMM: null pointer argument");
   MOE_CHECK_ARG(aligned16(a) && aligned16(w) && aligned16(out) && aligned16(aux_out) && aligned16(aux_in),
                 "grouped GEMM: pointers must be 16-byte aligned");
@@ -538,6 +701,7 @@ static int mgrouped_common(const void* a, const void* w, void* out, void* aux_ou
   MOE_CHECK_ARG(dtype == MOE_DTYPE_BF16 || dtype == MOE_DTYPE_F16, "grouped GEMM: unknown dtype %d", dtype);
   GemmArgs args{};
   args.mtile_expert = mtile_expert;
+  args.tile_pairs = tile_pairs;
   args.num_mtiles = num_mtiles;
   args.num_experts = E;
   args.n_dim = N;
@@ -549,15 +713,18 @@ static int mgrouped_common(const void* a, const void* w, void* out, void* aux_ou
   args.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bn = pick_bn(N);
-  if (dtype == MOE_DTYPE_BF16) {
-    return bn == 256 ? mgrouped_dispatch<__nv_bfloat16, 256>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s)
-                     : mgrouped_dispatch<__nv_bfloat16, 128>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s);
-  }
-  return bn == 256 ? mgrouped_dispatch<__half, 256>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s)
-                   : mgrouped_dispatch<__half, 128>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s);
+  const bool pairs = tile_pairs != nullptr && use_cta_pairs();
+#define MOE_MG(TYPE)                                                                                                  \
+  (pairs ? (bn == 256 ? mgrouped_dispatch<TYPE, 256, 2>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s) \
+                      : mgrouped_dispatch<TYPE, 128, 2>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s)) \
+         : (bn == 256 ? mgrouped_dispatch<TYPE, 256, 1>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s) \
+                      : mgrouped_dispatch<TYPE, 128, 1>(a, w, padded_rows, K, N, E, w_transposed, epi, args, dtype, s)))
+  if (dtype == MOE_DTYPE_BF16) return MOE_MG(__nv_bfloat16);
+  return MOE_MG(__half);
+#undef MOE_MG
 }
 
-template <typename T, int BN>
+template <typename T, int BN, int CTAS>
 static int kgrouped_dispatch(const void* a, const void* b, int64_t padded_rows, int M, int N, const GemmArgs& args,
                              int dtype, cudaStream_t stream) {
   CUtensorMap ta, tb;
@@ -572,7 +739,7 @@ static int kgrouped_dispatch(const void* a, const void* b, int64_t padded_rows, 
     int rc = make_tmap(&tb, dtype, b, 2, dims, box);
     if (rc != MOE_OK) return rc;
   }
-  return launch<T, BN, false, false, EPI_ACT, true>(ta, tb, args, sm_count(), stream);
+  return launch<T, BN, false, false, EPI_ACT, true, CTAS>(ta, tb, args, stream);
 }
 
 }  // namespace moe
@@ -580,22 +747,24 @@ static int kgrouped_dispatch(const void* a, const void* b, int64_t padded_rows, 
 using namespace moe;
 
 extern "C" int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act, const int32_t* mtile_expert,
-                                 const int32_t* num_mtiles, int64_t padded_rows, int K, int N, int num_experts,
-                                 int w_transposed, int act, int dtype, int32_t* status, void* stream) {
+                                 const int32_t* tile_pairs, const int32_t* num_mtiles, int64_t padded_rows, int K,
+                                 int N, int num_experts, int w_transposed, int act, int dtype, int32_t* status,
+                                 void* stream) {
   MOE_CHECK_ARG(act >= MOE_ACT_NONE && act <= MOE_ACT_GEGLU, "moe_mgrouped_gemm: unknown activation %d", act);
   const bool glu = act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU;
-  return mgrouped_common(a, w, out, glu ? pre_act : nullptr, nullptr, mtile_expert, num_mtiles, padded_rows, K, N,
-                         num_experts, w_transposed, glu ? EPI_GLU : EPI_ACT, act, dtype, status, stream);
+  return mgrouped_common(a, w, out, glu ? pre_act : nullptr, nullptr, mtile_expert, tile_pairs, num_mtiles,
+                         padded_rows, K, N, num_experts, w_transposed, glu ? EPI_GLU : EPI_ACT, act, dtype, status,
+                         stream);
 }
 
 extern "C" int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, void* d_pre,
-                                      const int32_t* mtile_expert, const int32_t* num_mtiles, int64_t padded_rows,
-                                      int K, int N, int num_experts, int act, int dtype, int32_t* status,
-                                      void* stream) {
+                                      const int32_t* mtile_expert, const int32_t* tile_pairs,
+                                      const int32_t* num_mtiles, int64_t padded_rows, int K, int N, int num_experts,
+                                      int act, int dtype, int32_t* status, void* stream) {
   MOE_CHECK_ARG(act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU, "moe_mgrouped_gemm_dglu: activation %d is not a GLU", act);
   MOE_CHECK_ARG(pre_act != nullptr, "moe_mgrouped_gemm_dglu: pre_act is null");
-  return mgrouped_common(g, w, d_pre, nullptr, pre_act, mtile_expert, num_mtiles, padded_rows, K, N, num_experts, 1,
-                         EPI_DGLU, act, dtype, status, stream);
+  return mgrouped_common(g, w, d_pre, nullptr, pre_act, mtile_expert, tile_pairs, num_mtiles, padded_rows, K, N,
+                         num_experts, 1, EPI_DGLU, act, dtype, status, stream);
 }
 
 extern "C" int moe_kgrouped_gemm(const void* a, const void* b, void* dw, const int32_t* pad_offsets,
@@ -621,10 +790,13 @@ extern "C" int moe_kgrouped_gemm(const void* a, const void* b, void* dw, const i
   args.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bn = pick_bn(N);
-  if (dtype == MOE_DTYPE_BF16) {
-    return bn == 256 ? kgrouped_dispatch<__nv_bfloat16, 256>(a, b, padded_rows, M, N, args, dtype, s)
-                     : kgrouped_dispatch<__nv_bfloat16, 128>(a, b, padded_rows, M, N, args, dtype, s);
-  }
-  return bn == 256 ? kgrouped_dispatch<__half, 256>(a, b, padded_rows, M, N, args, dtype, s)
-                   : kgrouped_dispatch<__half, 128>(a, b, padded_rows, M, N, args, dtype, s);
+  const bool pairs = use_cta_pairs();
+#define MOE_KG(TYPE)                                                                              \
+  (pairs ? (bn == 256 ? kgrouped_dispatch<TYPE, 256, 2>(a, b, padded_rows, M, N, args, dtype, s)  \
+                      : kgrouped_dispatch<TYPE, 128, 2>(a, b, padded_rows, M, N, args, dtype, s)) \
+         : (bn == 256 ? kgrouped_dispatch<TYPE, 256, 1>(a, b, padded_rows, M, N, args, dtype, s)  \
+                      : kgrouped_dispatch<TYPE, 128, 1>(a, b, padded_rows, M, N, args, dtype, s)))
+  if (dtype == MOE_DTYPE_BF16) return MOE_KG(__nv_bfloat16);
+  return MOE_KG(__half);
+#undef MOE_KG
 }

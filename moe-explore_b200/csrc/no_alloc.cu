@@ -55,7 +55,8 @@ extern "C" size_t moe_routing_static_scratch_bytes(void) { return kStaticScratch
 extern "C" int moe_routing_metadata_static(const int64_t* expert_idx, int64_t num_rows, int num_experts,
                                            int32_t* group_indices, int64_t* perm, int32_t* pad_offsets,
                                            int32_t* row_src, int32_t* dst_row, int32_t* mtile_expert,
-                                           int32_t* num_mtiles, int32_t* status, void* stream) {
+                                           int32_t* tile_pairs, int32_t* num_mtiles, int32_t* status,
+                                           void* stream) {
   if (num_rows < 0 || num_experts <= 0) {
     moe::set_error("moe_routing_metadata_static: bad sizes num_rows=%lld num_experts=%d", (long long)num_rows,
                    num_experts);
@@ -73,5 +74,5 @@ extern "C" int moe_routing_metadata_static(const int64_t* expert_idx, int64_t nu
   const int rc = scratch_for_current_device(&scratch);
   if (rc != MOE_OK) return rc;
   return moe_routing_metadata(expert_idx, num_rows, num_experts, group_indices, perm, pad_offsets, row_src, dst_row,
-                              mtile_expert, num_mtiles, status, scratch, kStaticScratchBytes, stream);
+                              mtile_expert, tile_pairs, num_mtiles, status, scratch, kStaticScratchBytes, stream);
 }

@@ -72,14 +72,31 @@ chunk_histogram_kernel(const int64_t* __restrict__ ids, int64_t R, int E, int32_
   for (int e = lane; e < E; e += 32) chunk_hist[chunk * E + e] = cnt[e];
 }
 
+// Pair entry layout: bits 0-19 first tile, bits 20-30 expert, bit 31 "the pair has a second tile"
+// (so one load tells a CTA pair everything about its next work item).
+// Tile -> expert map and the pair list for expert e, whose padded rows start at `row_begin` and span
+// `padded` rows; its pairs start at index `pair_begin`.
+__device__ __forceinline__ void write_tile_maps(int e, int32_t row_begin, int32_t padded, int32_t pair_begin,
+                                                int32_t* __restrict__ mtile_expert, int32_t* __restrict__ tile_pairs) {
+  const int first = row_begin / MOE_TILE_M;
+  const int last = first + padded / MOE_TILE_M;
+  for (int m = first; m < last; ++m) mtile_expert[m] = e;
+  if (tile_pairs != nullptr) {
+    for (int m = first, p = pair_begin; m < last; m += 2, ++p)
+      tile_pairs[p] = static_cast<int32_t>(static_cast<uint32_t>(m) | (static_cast<uint32_t>(e) << 20) |
+                                           (m + 1 < last ? 0x80000000u : 0u));
+  }
+}
+
 // One CTA, one thread per expert (E <= 1024).
 __global__ void __launch_bounds__(kMaxExperts)
 scan_offsets_kernel(const int32_t* __restrict__ chunk_hist, int32_t* __restrict__ chunk_off, int64_t nchunks, int E,
                     int32_t* __restrict__ group_indices,
                     int32_t* __restrict__ pad_offsets, int32_t* __restrict__ mtile_expert,
-                    int32_t* __restrict__ num_mtiles) {
+                    int32_t* __restrict__ tile_pairs, int32_t* __restrict__ num_mtiles) {
   __shared__ int32_t sh_a[kMaxExperts];
   __shared__ int32_t sh_b[kMaxExperts];
+  __shared__ int32_t sh_c[kMaxExperts];
   const int e = threadIdx.x;
   int32_t total = 0;
   if (e < E) {
@@ -97,28 +114,30 @@ scan_offsets_kernel(const int32_t* __restrict__ chunk_hist, int32_t* __restrict_
     }
   }
   const int32_t padded = (total + MOE_TILE_M - 1) / MOE_TILE_M * MOE_TILE_M;
+  const int32_t pairs = (padded / MOE_TILE_M + 1) / 2;  // row tiles of one expert, two at a time
   sh_a[e] = e < E ? total : 0;
   sh_b[e] = e < E ? padded : 0;
+  sh_c[e] = e < E ? pairs : 0;
   __syncthreads();
-  // Hillis-Steele inclusive scan over experts for both sequences.
+  // Hillis-Steele inclusive scan over experts for the three sequences.
   for (int off = 1; off < kMaxExperts; off <<= 1) {
-    int32_t a = 0, b = 0;
-    if (e >= off) { a = sh_a[e - off]; b = sh_b[e - off]; }
+    int32_t a = 0, b = 0, c = 0;
+    if (e >= off) { a = sh_a[e - off]; b = sh_b[e - off]; c = sh_c[e - off]; }
     __syncthreads();
     sh_a[e] += a;
     sh_b[e] += b;
+    sh_c[e] += c;
     __syncthreads();
   }
   if (e < E) {
     group_indices[e + 1] = sh_a[e];
     pad_offsets[e + 1] = sh_b[e];
     if (e == 0) { group_indices[0] = 0; pad_offsets[0] = 0; }
-    if (mtile_expert != nullptr) {
-      const int first = (sh_b[e] - padded) / MOE_TILE_M;
-      const int last = sh_b[e] / MOE_TILE_M;
-      for (int m = first; m < last; ++m) mtile_expert[m] = e;
+    if (mtile_expert != nullptr) write_tile_maps(e, sh_b[e] - padded, padded, sh_c[e] - pairs, mtile_expert, tile_pairs);
+    if (num_mtiles != nullptr && e == E - 1) {
+      num_mtiles[0] = sh_b[e] / MOE_TILE_M;
+      num_mtiles[1] = sh_c[e];
     }
-    if (num_mtiles != nullptr && e == E - 1) *num_mtiles = sh_b[e] / MOE_TILE_M;
   }
 }
 
@@ -160,30 +179,36 @@ place_rows_kernel(const int64_t* __restrict__ ids, int64_t R, int E, const int32
 // the padded prefix, then all threads fill the row maps.
 __global__ void __launch_bounds__(kMaxExperts)
 layout_from_groups_kernel(const int32_t* __restrict__ group_indices, int64_t R, int E, int32_t* __restrict__ pad_offsets,
-                          int32_t* __restrict__ mtile_expert, int32_t* __restrict__ num_mtiles) {
+                          int32_t* __restrict__ mtile_expert, int32_t* __restrict__ tile_pairs,
+                          int32_t* __restrict__ num_mtiles) {
   __shared__ int32_t sh_b[kMaxExperts];
+  __shared__ int32_t sh_c[kMaxExperts];
   const int e = threadIdx.x;
   int32_t padded = 0;
   if (e < E) {
     const int32_t cnt = group_indices[e + 1] - group_indices[e];
     padded = (cnt + MOE_TILE_M - 1) / MOE_TILE_M * MOE_TILE_M;
   }
+  const int32_t pairs = (padded / MOE_TILE_M + 1) / 2;
   sh_b[e] = padded;
+  sh_c[e] = pairs;
   __syncthreads();
   for (int off = 1; off < kMaxExperts; off <<= 1) {
-    int32_t b = 0;
-    if (e >= off) b = sh_b[e - off];
+    int32_t b = 0, c = 0;
+    if (e >= off) { b = sh_b[e - off]; c = sh_c[e - off]; }
     __syncthreads();
     sh_b[e] += b;
+    sh_c[e] += c;
     __syncthreads();
   }
   if (e < E) {
     pad_offsets[e + 1] = sh_b[e];
     if (e == 0) pad_offsets[0] = 0;
-    if (mtile_expert != nullptr) {
-      for (int m = (sh_b[e] - padded) / MOE_TILE_M; m < sh_b[e] / MOE_TILE_M; ++m) mtile_expert[m] = e;
+    if (mtile_expert != nullptr) write_tile_maps(e, sh_b[e] - padded, padded, sh_c[e] - pairs, mtile_expert, tile_pairs);
+    if (num_mtiles != nullptr && e == E - 1) {
+      num_mtiles[0] = sh_b[e] / MOE_TILE_M;
+      num_mtiles[1] = sh_c[e];
     }
-    if (num_mtiles != nullptr && e == E - 1) *num_mtiles = sh_b[e] / MOE_TILE_M;
   }
 }
 
@@ -226,20 +251,21 @@ extern "C" size_t moe_routing_workspace_bytes(int64_t num_rows, int num_experts)
 
 extern "C" int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows, int num_experts,
                                     int32_t* group_indices, int64_t* perm, int32_t* pad_offsets, int32_t* row_src,
-                                    int32_t* dst_row, int32_t* mtile_expert, int32_t* num_mtiles, int32_t* status,
-                                    void* workspace, size_t workspace_bytes, void* stream) {
+                                    int32_t* dst_row, int32_t* mtile_expert, int32_t* tile_pairs,
+                                    int32_t* num_mtiles, int32_t* status, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
   MOE_CHECK_ARG(num_rows >= 0, "moe_routing_metadata: num_rows=%lld is negative", (long long)num_rows);
   MOE_CHECK_ARG(num_experts > 0, "moe_routing_metadata: num_experts=%d must be positive", num_experts);
   if (num_experts > kMaxExperts) {
     set_error("moe_routing_metadata: num_experts=%d exceeds the supported maximum %d", num_experts, kMaxExperts);
     return MOE_ERR_UNSUPPORTED;
   }
-  MOE_CHECK_ARG(num_rows + (int64_t)num_experts * MOE_TILE_M < (1ll << 31),
-                "moe_routing_metadata: num_rows=%lld does not fit 32-bit row offsets", (long long)num_rows);
+  MOE_CHECK_ARG(moe_mtiles_bound(num_rows, num_experts) < (1ll << 20),
+                "moe_routing_metadata: num_rows=%lld needs more than 2^20 row tiles", (long long)num_rows);
   MOE_CHECK_ARG(group_indices && pad_offsets, "moe_routing_metadata: group_indices and pad_offsets are required");
   MOE_CHECK_ARG(num_rows == 0 || expert_idx != nullptr, "moe_routing_metadata: expert_idx is null");
-  MOE_CHECK_ARG((mtile_expert == nullptr) == (num_mtiles == nullptr),
-                "moe_routing_metadata: mtile_expert and num_mtiles go together");
+  MOE_CHECK_ARG((mtile_expert == nullptr) == (num_mtiles == nullptr) && (tile_pairs == nullptr || mtile_expert != nullptr),
+                "moe_routing_metadata: mtile_expert, tile_pairs and num_mtiles go together");
   MOE_CHECK_ARG(workspace != nullptr && workspace_bytes >= moe_routing_workspace_bytes(num_rows, num_experts),
                 "moe_routing_metadata: workspace of %zu bytes is smaller than the %zu required", workspace_bytes,
                 moe_routing_workspace_bytes(num_rows, num_experts));
@@ -259,7 +285,7 @@ extern "C" int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows,
     MOE_CUDA(cudaGetLastError());
   }
   scan_offsets_kernel<<<1, kMaxExperts, 0, s>>>(chunk_hist, chunk_off, chunks, num_experts, group_indices, pad_offsets,
-                                               mtile_expert, num_mtiles);
+                                               mtile_expert, tile_pairs, num_mtiles);
   MOE_CUDA(cudaGetLastError());
   if (chunks > 0 && (perm || row_src || dst_row)) {
     place_rows_kernel<<<blocks, kWarpsPerBlock * 32, sh, s>>>(expert_idx, num_rows, num_experts, chunk_off,
@@ -271,22 +297,24 @@ extern "C" int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows,
 
 extern "C" int moe_layout_from_groups(const int32_t* group_indices, int64_t num_rows, int num_experts,
                                       int32_t* pad_offsets, int32_t* row_src, int32_t* dst_row, int32_t* mtile_expert,
-                                      int32_t* num_mtiles, void* stream) {
+                                      int32_t* tile_pairs, int32_t* num_mtiles, void* stream) {
   MOE_CHECK_ARG(group_indices && pad_offsets, "moe_layout_from_groups: group_indices and pad_offsets are required");
   MOE_CHECK_ARG(num_rows >= 0 && num_experts > 0, "moe_layout_from_groups: bad sizes R=%lld E=%d", (long long)num_rows,
                 num_experts);
+  MOE_CHECK_ARG(moe_mtiles_bound(num_rows, num_experts) < (1ll << 20),
+                "moe_layout_from_groups: num_rows=%lld needs more than 2^20 row tiles", (long long)num_rows);
   if (num_experts > kMaxExperts) {
     set_error("moe_layout_from_groups: num_experts=%d exceeds the supported maximum %d", num_experts, kMaxExperts);
     return MOE_ERR_UNSUPPORTED;
   }
-  MOE_CHECK_ARG((mtile_expert == nullptr) == (num_mtiles == nullptr),
-                "moe_layout_from_groups: mtile_expert and num_mtiles go together");
+  MOE_CHECK_ARG((mtile_expert == nullptr) == (num_mtiles == nullptr) && (tile_pairs == nullptr || mtile_expert != nullptr),
+                "moe_layout_from_groups: mtile_expert, tile_pairs and num_mtiles go together");
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (row_src != nullptr) {
     MOE_CUDA(cudaMemsetAsync(row_src, 0xFF, moe_padded_rows_bound(num_rows, num_experts) * sizeof(int32_t), s));
   }
   layout_from_groups_kernel<<<1, kMaxExperts, 0, s>>>(group_indices, num_rows, num_experts, pad_offsets, mtile_expert,
-                                                     num_mtiles);
+                                                     tile_pairs, num_mtiles);
   MOE_CUDA(cudaGetLastError());
   if (num_rows > 0 && (row_src || dst_row)) {
     const int threads = 256;

@@ -28,16 +28,16 @@ SIGNATURES = {
     "moe_padded_rows_bound": (c_int64, [c_int64, c_int]),
     "moe_mtiles_bound": (c_int64, [c_int64, c_int]),
     "moe_routing_workspace_bytes": (c_size_t, [c_int64, c_int]),
-    "moe_routing_metadata": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 8 + [c_void_p, c_size_t, c_void_p]),
+    "moe_routing_metadata": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 9 + [c_void_p, c_size_t, c_void_p]),
     "moe_routing_static_scratch_bytes": (c_size_t, []),
-    "moe_routing_metadata_static": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 8 + [c_void_p]),
-    "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 5 + [c_void_p]),
+    "moe_routing_metadata_static": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 9 + [c_void_p]),
+    "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 6 + [c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_combine_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_combine_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
-    "moe_mgrouped_gemm": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "moe_mgrouped_gemm_dglu": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moe_mgrouped_gemm": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moe_mgrouped_gemm_dglu": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_kgrouped_gemm": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
 }
 
@@ -65,8 +65,9 @@ def _count(n: int) -> None:
 
 
 class _Timed:
-    def __init__(self, key: str):
+    def __init__(self, key: str, rows=None):
         self.key = key if PROFILE is not None else None
+        self.rows = rows
 
     def __enter__(self):
         if self.key is not None:
@@ -77,8 +78,14 @@ class _Timed:
     def __exit__(self, *exc):
         if self.key is not None:
             self.end.record()
-            PROFILE.setdefault(self.key, []).append((self.start, self.end))
+            PROFILE.setdefault(self.key, []).append((self.start, self.end, self.rows))
         return False
+
+
+def timed(key: str, rows=None):
+    """Context manager: CUDA-event bracket on the current stream, recorded under ``key`` while
+    ``PROFILE`` is a dict; free otherwise.  ``rows`` notes how many routed rows the section handled."""
+    return _Timed(key, rows)
 
 
 def load() -> ctypes.CDLL:
@@ -145,24 +152,26 @@ def check_status(status: torch.Tensor) -> None:
 
 
 def routing_metadata(expert_idx, num_experts, group_indices, perm, pad_offsets, row_src, dst_row, mtile_expert,
-                     num_mtiles, status, workspace):
+                     tile_pairs, num_mtiles, status, workspace):
     require_cuda(expert_idx)
     rc = load().moe_routing_metadata(_ptr(expert_idx), expert_idx.numel(), num_experts, _ptr(group_indices),
                                      _ptr(perm), _ptr(pad_offsets), _ptr(row_src), _ptr(dst_row),
-                                     _ptr(mtile_expert), _ptr(num_mtiles), _ptr(status), _ptr(workspace),
+                                     _ptr(mtile_expert), _ptr(tile_pairs), _ptr(num_mtiles), _ptr(status),
+                                     _ptr(workspace),
                                      workspace.numel() * workspace.element_size(), _stream())
     _check("moe_routing_metadata", rc)
     _count(3 if expert_idx.numel() > 0 else 1)
 
 
 def routing_metadata_static(expert_idx, num_experts, group_indices, perm, pad_offsets, row_src, dst_row, mtile_expert,
-                            num_mtiles, status):
+                            tile_pairs, num_mtiles, status):
     """Routing metadata with the library's built-in scratch: for callers that cannot allocate
     device memory.  Calls on one device must not overlap; see include/moe_sm100.h for the limits."""
     require_cuda(expert_idx)
     rc = load().moe_routing_metadata_static(_ptr(expert_idx), expert_idx.numel(), num_experts, _ptr(group_indices),
                                             _ptr(perm), _ptr(pad_offsets), _ptr(row_src), _ptr(dst_row),
-                                            _ptr(mtile_expert), _ptr(num_mtiles), _ptr(status), _stream())
+                                            _ptr(mtile_expert), _ptr(tile_pairs), _ptr(num_mtiles), _ptr(status),
+                                            _stream())
     _check("moe_routing_metadata_static", rc)
     _count(3 if expert_idx.numel() > 0 else 1)
 
@@ -171,76 +180,82 @@ def routing_workspace_bytes(num_rows: int, num_experts: int) -> int:
     return int(load().moe_routing_workspace_bytes(num_rows, num_experts))
 
 
-def layout_from_groups(group_indices, num_rows, num_experts, pad_offsets, row_src, dst_row, mtile_expert, num_mtiles):
+def layout_from_groups(group_indices, num_rows, num_experts, pad_offsets, row_src, dst_row, mtile_expert, tile_pairs,
+                       num_mtiles):
     require_cuda(group_indices)
     rc = load().moe_layout_from_groups(_ptr(group_indices), num_rows, num_experts, _ptr(pad_offsets), _ptr(row_src),
-                                       _ptr(dst_row), _ptr(mtile_expert), _ptr(num_mtiles), _stream())
+                                       _ptr(dst_row), _ptr(mtile_expert), _ptr(tile_pairs), _ptr(num_mtiles),
+                                       _stream())
     _check("moe_layout_from_groups", rc)
     _count(2 if num_rows > 0 else 1)
 
 
 def gather_rows(src, row_src, num_mtiles, dst, div):
     require_cuda(src, dst)
-    rc = load().moe_gather_rows(_ptr(src), src.size(0), _ptr(row_src), _ptr(num_mtiles), _ptr(dst), dst.size(0),
-                                src.size(1), div, dtype_code(src.dtype), _stream())
+    with _Timed("rows:gather"):
+        rc = load().moe_gather_rows(_ptr(src), src.size(0), _ptr(row_src), _ptr(num_mtiles), _ptr(dst), dst.size(0),
+                                    src.size(1), div, dtype_code(src.dtype), _stream())
     _check("moe_gather_rows", rc)
     _count(1)
 
 
 def unpad_rows(src, dst_row, out):
     require_cuda(src, out)
-    rc = load().moe_unpad_rows(_ptr(src), _ptr(dst_row), _ptr(out), out.size(0), out.size(1),
-                               dtype_code(src.dtype), _stream())
+    with _Timed("rows:unpad"):
+        rc = load().moe_unpad_rows(_ptr(src), _ptr(dst_row), _ptr(out), out.size(0), out.size(1),
+                                   dtype_code(src.dtype), _stream())
     _check("moe_unpad_rows", rc)
     _count(1)
 
 
 def combine_topk(ys, scores, dst_row, out, topk):
     require_cuda(ys, out)
-    rc = load().moe_combine_topk(_ptr(ys), _ptr(scores), _ptr(dst_row), _ptr(out), out.size(0), topk, out.size(1),
-                                 dtype_code(ys.dtype), _stream())
+    with _Timed("rows:combine"):
+        rc = load().moe_combine_topk(_ptr(ys), _ptr(scores), _ptr(dst_row), _ptr(out), out.size(0), topk, out.size(1),
+                                     dtype_code(ys.dtype), _stream())
     _check("moe_combine_topk", rc)
     _count(1)
 
 
 def combine_bwd(dout, scores, ys, row_src, num_mtiles, gs, dscores, topk):
     require_cuda(dout, ys, gs)
-    rc = load().moe_combine_bwd(_ptr(dout), _ptr(scores), _ptr(ys), _ptr(row_src), _ptr(num_mtiles), _ptr(gs),
-                                _ptr(dscores), dout.size(0), topk, gs.size(0), dout.size(1), dtype_code(dout.dtype),
-                                _stream())
+    with _Timed("rows:combine_bwd"):
+        rc = load().moe_combine_bwd(_ptr(dout), _ptr(scores), _ptr(ys), _ptr(row_src), _ptr(num_mtiles), _ptr(gs),
+                                    _ptr(dscores), dout.size(0), topk, gs.size(0), dout.size(1), dtype_code(dout.dtype),
+                                    _stream())
     _check("moe_combine_bwd", rc)
     _count(1)
 
 
-def mgrouped_gemm(a, w, out, pre_act, mtile_expert, num_mtiles, w_transposed, act, status=None):
+def mgrouped_gemm(a, w, out, pre_act, mtile_expert, tile_pairs, num_mtiles, w_transposed, act, status=None, rows=None):
     require_cuda(a, w, out)
     E = w.size(0)
     K = a.size(1)
     N = w.size(1) if w_transposed else w.size(2)
     key = "mgrouped_gemm:" + ("glu" if act in ("swiglu", "geglu") else ("wt" if w_transposed else "plain"))
-    with _Timed(key):
+    with _Timed(key, rows):
         rc = load().moe_mgrouped_gemm(_ptr(a), _ptr(w), _ptr(out), _ptr(pre_act), _ptr(mtile_expert),
-                                      _ptr(num_mtiles), a.size(0), K, N, E, 1 if w_transposed else 0, ACT_CODES[act],
+                                      _ptr(tile_pairs), _ptr(num_mtiles), a.size(0), K, N, E, 1 if w_transposed else 0, ACT_CODES[act],
                                       dtype_code(a.dtype), _ptr(status), _stream())
     _check("moe_mgrouped_gemm", rc)
     _count(1)
 
 
-def mgrouped_gemm_dglu(g, w, pre_act, d_pre, mtile_expert, num_mtiles, act, status=None):
+def mgrouped_gemm_dglu(g, w, pre_act, d_pre, mtile_expert, tile_pairs, num_mtiles, act, status=None, rows=None):
     require_cuda(g, w, pre_act, d_pre)
     E, N, K = w.shape
-    with _Timed("mgrouped_gemm:dglu"):
+    with _Timed("mgrouped_gemm:dglu", rows):
         rc = load().moe_mgrouped_gemm_dglu(_ptr(g), _ptr(w), _ptr(pre_act), _ptr(d_pre), _ptr(mtile_expert),
-                                           _ptr(num_mtiles), g.size(0), K, N, E, ACT_CODES[act], dtype_code(g.dtype),
+                                           _ptr(tile_pairs), _ptr(num_mtiles), g.size(0), K, N, E, ACT_CODES[act], dtype_code(g.dtype),
                                            _ptr(status), _stream())
     _check("moe_mgrouped_gemm_dglu", rc)
     _count(1)
 
 
-def kgrouped_gemm(a, b, dw, pad_offsets, status=None):
+def kgrouped_gemm(a, b, dw, pad_offsets, status=None, rows=None, tag="dw"):
     require_cuda(a, b, dw)
     E, M, N = dw.shape
-    with _Timed("kgrouped_gemm"):
+    with _Timed("kgrouped_gemm:" + tag, rows):
         rc = load().moe_kgrouped_gemm(_ptr(a), _ptr(b), _ptr(dw), _ptr(pad_offsets), a.size(0), M, N, E,
                                       dtype_code(a.dtype), _ptr(status), _stream())
     _check("moe_kgrouped_gemm", rc)

@@ -40,9 +40,11 @@ class ExpertCompute(torch.autograd.Function):
         _native.gather_rows(x, plan.row_src, plan.num_mtiles, xs, plan.topk)
         hidden = new(rp, inter)
         pre_act = new(rp, n1) if is_glu(act) else None
-        _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.num_mtiles, False, act, plan.status)
+        _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act, plan.status,
+                              rows=plan.num_rows)
         ys = new(rp, d)
-        _native.mgrouped_gemm(hidden, weight2, ys, None, plan.mtile_expert, plan.num_mtiles, False, None, plan.status)
+        _native.mgrouped_gemm(hidden, weight2, ys, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status,
+                              rows=plan.num_rows)
         out = new(T, d)
         _native.combine_topk(ys, scores, plan.dst_row, out, plan.topk)
 
@@ -67,15 +69,17 @@ class ExpertCompute(torch.autograd.Function):
         d_scores = new(T, plan.topk)
         _native.combine_bwd(grad_out, scores, ys, plan.row_src, plan.num_mtiles, gs, d_scores, plan.topk)
         d_pre = new(rp, pre_act.size(1))
-        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.num_mtiles, act, plan.status)
+        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, act, plan.status,
+                                   rows=plan.num_rows)
         dxs = new(rp, d)
-        _native.mgrouped_gemm(d_pre, weight1, dxs, None, plan.mtile_expert, plan.num_mtiles, True, None, plan.status)
+        _native.mgrouped_gemm(d_pre, weight1, dxs, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, True, None, plan.status,
+                              rows=plan.num_rows)
         dx = new(T, d)
         _native.combine_topk(dxs, None, plan.dst_row, dx, plan.topk)
         d_w1 = torch.empty_like(weight1)
-        _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status)
+        _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status, rows=plan.num_rows, tag="dw1")
         d_w2 = torch.empty_like(weight2)
-        _native.kgrouped_gemm(hidden, gs, d_w2, plan.pad_offsets, plan.status)
+        _native.kgrouped_gemm(hidden, gs, d_w2, plan.pad_offsets, plan.status, rows=plan.num_rows, tag="dw2")
         return dx, d_scores, d_w1, d_w2, None, None
 
 

@@ -73,9 +73,11 @@ class NativeOps:
         _native.gather_rows(recv_x, plan.row_src, plan.num_mtiles, xs, 1)
         hidden = new(rp, weight2.size(1))
         pre_act = new(rp, weight1.size(2))
-        _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.num_mtiles, False, act, plan.status)
+        _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act, plan.status,
+                              rows=plan.num_rows)
         ys = new(rp, d)
-        _native.mgrouped_gemm(hidden, weight2, ys, None, plan.mtile_expert, plan.num_mtiles, False, None, plan.status)
+        _native.mgrouped_gemm(hidden, weight2, ys, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status,
+                              rows=plan.num_rows)
         y = new(recv_x.size(0), d)
         _native.unpad_rows(ys, plan.dst_row, y)
         return y, (plan, xs, hidden, pre_act)
@@ -88,13 +90,15 @@ class NativeOps:
         gs = new(rp, d)
         _native.gather_rows(recv_g, plan.row_src, plan.num_mtiles, gs, 1)
         d_pre = new(rp, pre_act.size(1))
-        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.num_mtiles, act, plan.status)
+        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, act, plan.status,
+                                   rows=plan.num_rows)
         dxs = new(rp, d)
-        _native.mgrouped_gemm(d_pre, weight1, dxs, None, plan.mtile_expert, plan.num_mtiles, True, None, plan.status)
+        _native.mgrouped_gemm(d_pre, weight1, dxs, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, True, None, plan.status,
+                              rows=plan.num_rows)
         d_w1 = torch.empty_like(weight1)
-        _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status)
+        _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status, rows=plan.num_rows, tag="dw1")
         d_w2 = torch.empty_like(weight2)
-        _native.kgrouped_gemm(hidden, gs, d_w2, plan.pad_offsets, plan.status)
+        _native.kgrouped_gemm(hidden, gs, d_w2, plan.pad_offsets, plan.status, rows=plan.num_rows, tag="dw2")
         dx = new(recv_g.size(0), d)
         _native.unpad_rows(dxs, plan.dst_row, dx)
         return dx, d_w1, d_w2
@@ -138,7 +142,8 @@ def build_dispatch_layout(indices: torch.Tensor, num_experts: int, group, ops) -
 
 def _exchange(rows: torch.Tensor, in_splits, out_splits, group) -> torch.Tensor:
     out = torch.empty(sum(out_splits), rows.size(1), dtype=rows.dtype, device=rows.device)
-    dist.all_to_all_single(out, rows, output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
+    with _native.timed("ep:all_to_all"):
+        dist.all_to_all_single(out, rows, output_split_sizes=out_splits, input_split_sizes=in_splits, group=group)
     return out
 
 
@@ -190,6 +195,7 @@ def ep_expert_compute(x: torch.Tensor, scores: torch.Tensor, indices: torch.Tens
         _native.require_cuda(x, scores, indices, local_weight1, local_weight2)
         ops = NativeOps()
     group = group if group is not None else dist.group.WORLD
-    layout = build_dispatch_layout(indices, num_experts, group, ops)
+    with _native.timed("ep:layout"):
+        layout = build_dispatch_layout(indices, num_experts, group, ops)
     return EPExpertCompute.apply(x, scores, local_weight1.contiguous(), local_weight2.contiguous(), layout,
                                  indices.size(1), str(act), group, ops)

@@ -26,7 +26,8 @@ class RoutingPlan:
     row_src: torch.Tensor         # int32 [RP] flat position held by padded row p, -1 for padding
     dst_row: torch.Tensor         # int32 [R]  padded row of flat position j
     mtile_expert: torch.Tensor    # int32 [RP/128] expert of each 128-row tile
-    num_mtiles: torch.Tensor      # int32 [1]  tiles in use
+    tile_pairs: torch.Tensor      # int32 [RP/128] first tile of each same-expert tile pair (bit 31: pair has two tiles)
+    num_mtiles: torch.Tensor      # int32 [2]  {tiles in use, tile pairs in use}
     status: torch.Tensor          # int32 [1]  device status word shared by the kernels of this plan
 
     def check(self) -> None:
@@ -45,7 +46,8 @@ def _alloc(num_rows: int, num_experts: int, device, want_perm: bool):
         row_src=torch.empty(rp, **i32),
         dst_row=torch.empty(num_rows, **i32),
         mtile_expert=torch.empty(rp // _native.TILE_M, **i32),
-        num_mtiles=torch.empty(1, **i32),
+        tile_pairs=torch.empty(rp // _native.TILE_M, **i32),
+        num_mtiles=torch.empty(2, **i32),
         status=torch.zeros(1, **i32),
     )
 
@@ -59,8 +61,8 @@ def build_routing_plan(expert_indices: torch.Tensor, num_experts: int, topk: int
     ws = torch.empty(max(_native.routing_workspace_bytes(flat.numel(), num_experts), 16), dtype=torch.uint8,
                      device=flat.device)
     _native.routing_metadata(flat, num_experts, bufs["group_indices"], bufs["perm"], bufs["pad_offsets"],
-                             bufs["row_src"], bufs["dst_row"], bufs["mtile_expert"], bufs["num_mtiles"],
-                             bufs["status"], ws)
+                             bufs["row_src"], bufs["dst_row"], bufs["mtile_expert"], bufs["tile_pairs"],
+                             bufs["num_mtiles"], bufs["status"], ws)
     return RoutingPlan(num_rows=flat.numel(), num_experts=num_experts, topk=topk, **bufs)
 
 
@@ -72,5 +74,5 @@ def plan_from_groups(group_indices: torch.Tensor, num_rows: int) -> RoutingPlan:
     bufs = _alloc(num_rows, num_experts, group_indices.device, want_perm=False)
     bufs["group_indices"] = group_indices.contiguous()
     _native.layout_from_groups(bufs["group_indices"], num_rows, num_experts, bufs["pad_offsets"], bufs["row_src"],
-                               bufs["dst_row"], bufs["mtile_expert"], bufs["num_mtiles"])
+                               bufs["dst_row"], bufs["mtile_expert"], bufs["tile_pairs"], bufs["num_mtiles"])
     return RoutingPlan(num_rows=num_rows, num_experts=num_experts, topk=1, **bufs)

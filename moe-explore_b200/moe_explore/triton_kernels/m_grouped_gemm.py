@@ -62,7 +62,7 @@ def m_grouped_gemm(token: torch.Tensor, params: MGroupedGEMMParams, autotune_mod
         _native.gather_rows(token, plan.row_src, plan.num_mtiles, a, 1)
 
     y = torch.empty(plan.padded_rows, out_cols, dtype=token.dtype, device=token.device)
-    _native.mgrouped_gemm(a, params.weight.contiguous(), y, None, plan.mtile_expert, plan.num_mtiles, False, act,
+    _native.mgrouped_gemm(a, params.weight.contiguous(), y, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act,
                           plan.status)
     if params.scatter:
         # out[perm[r]] = y[dst_row[r]]

@@ -150,7 +150,7 @@ def test_kgrouped_weight_gradient_gemm(E, M, N, rows, native):
     if E == 16:
         idx = idx // 4 * 4   # leaves most experts empty
     plan = build_routing_plan(idx.cuda(), E, 1)
-    n = int(plan.num_mtiles.item()) * 128
+    n = int(plan.num_mtiles[0].item()) * 128
     a = torch.zeros(plan.padded_rows, M, dtype=torch.bfloat16, device="cuda")
     b = torch.zeros(plan.padded_rows, N, dtype=torch.bfloat16, device="cuda")
     valid = (plan.row_src[:n] >= 0)[:, None]

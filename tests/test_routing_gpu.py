@@ -24,8 +24,21 @@ def _check_against_oracle(idx, E):
     assert torch.equal(plan.group_indices.cpu(), ref.group_indices)
     assert plan.perm.dtype == torch.int64 and torch.equal(plan.perm.cpu(), ref.indices)
     po, row_src, dst_row, mte = O.padded_layout(idx.cpu(), E)
-    n = int(plan.num_mtiles.item())
+    n, num_pairs = plan.num_mtiles.tolist()
     assert n == int(po[-1]) // 128
+    # tile pairs: every tile appears exactly once, both tiles of a pair belong to the same expert
+    pairs = plan.tile_pairs[:num_pairs].cpu().tolist()
+    seen = []
+    for info in pairs:
+        first, expert, second = info & 0xFFFFF, (info >> 20) & 0x7FF, (info >> 31) & 1
+        assert expert == int(mte[first])
+        seen.append(first)
+        if second:
+            assert int(mte[first]) == int(mte[first + 1])
+            seen.append(first + 1)
+        else:
+            assert first + 1 == n or int(mte[first + 1]) != int(mte[first])
+    assert seen == list(range(n))
     assert torch.equal(plan.pad_offsets.cpu(), po)
     assert torch.equal(plan.row_src[: n * 128].cpu(), row_src)
     assert torch.equal(plan.dst_row.cpu(), dst_row)
@@ -108,4 +121,4 @@ def test_out_of_range_ids_are_flagged_not_placed(native):
 def test_empty_input(native):
     plan = _plan(torch.zeros(0, 2, dtype=torch.int64), 8, 2)
     assert plan.group_indices.cpu().tolist() == [0] * 9
-    assert int(plan.num_mtiles.item()) == 0
+    assert plan.num_mtiles.tolist() == [0, 0]

@@ -24,7 +24,8 @@ def _outputs(num_rows, num_experts, native):
                 perm=torch.full((num_rows,), -3, dtype=torch.int64, device="cuda"),
                 pad_offsets=torch.full((num_experts + 1,), -3, **i32), row_src=torch.full((rp,), -3, **i32),
                 dst_row=torch.full((num_rows,), -3, **i32), mtile_expert=torch.full((rp // 128,), -3, **i32),
-                num_mtiles=torch.full((1,), -3, **i32), status=torch.zeros(1, **i32))
+                tile_pairs=torch.full((rp // 128,), -3, **i32), num_mtiles=torch.full((2,), -3, **i32),
+                status=torch.zeros(1, **i32))
 
 
 def _run_both(idx, num_experts, native):
@@ -33,12 +34,13 @@ def _run_both(idx, num_experts, native):
     b = _outputs(flat.numel(), num_experts, native)
     ws = torch.empty(native.routing_workspace_bytes(flat.numel(), num_experts), dtype=torch.uint8, device="cuda")
     native.routing_metadata(flat, num_experts, a["group_indices"], a["perm"], a["pad_offsets"], a["row_src"],
-                            a["dst_row"], a["mtile_expert"], a["num_mtiles"], a["status"], ws)
+                            a["dst_row"], a["mtile_expert"], a["tile_pairs"], a["num_mtiles"], a["status"], ws)
     native.routing_metadata_static(flat, num_experts, b["group_indices"], b["perm"], b["pad_offsets"], b["row_src"],
-                                   b["dst_row"], b["mtile_expert"], b["num_mtiles"], b["status"])
+                                   b["dst_row"], b["mtile_expert"], b["tile_pairs"], b["num_mtiles"], b["status"])
     torch.cuda.synchronize()
-    n = int(a["num_mtiles"].item())
-    assert n == int(b["num_mtiles"].item())
+    n, pairs = a["num_mtiles"].tolist()
+    assert [n, pairs] == b["num_mtiles"].tolist()
+    assert torch.equal(a["tile_pairs"][:pairs], b["tile_pairs"][:pairs])
     for key in ("group_indices", "perm", "pad_offsets", "dst_row", "status"):
         assert torch.equal(a[key], b[key]), key
     assert torch.equal(a["row_src"][: n * 128], b["row_src"][: n * 128])
@@ -67,5 +69,5 @@ def test_static_scratch_entry_rejects_oversized_problems(native):
     out = _outputs(rows, experts, native)
     with pytest.raises(native.MoeNativeError, match="built-in scratch holds"):
         native.routing_metadata_static(idx, experts, out["group_indices"], out["perm"], out["pad_offsets"],
-                                       out["row_src"], out["dst_row"], out["mtile_expert"], out["num_mtiles"],
-                                       out["status"])
+                                       out["row_src"], out["dst_row"], out["mtile_expert"], out["tile_pairs"],
+                                       out["num_mtiles"], out["status"])
