@@ -201,8 +201,12 @@ def run_ours(args):
     if with_router:
         inp["router_weight"].requires_grad_()
 
+    ep_context = None
     if world > 1:
-        from moe_explore.expert_parallel import ep_expert_compute
+        from moe_explore.expert_parallel import EPContext, ep_expert_compute
+
+        if args.ep_mode == "peer":
+            ep_context = EPContext(dist.group.WORLD, w["T"], w["d"], w["k"], x.dtype, device)
 
     def step(x_in, g_in):
         """One forward + backward on device-resident inputs; returns (out, dx)."""
@@ -224,7 +228,7 @@ def run_ours(args):
         else:
             logits = inp["logits"].requires_grad_()
             scores, idx = scores_from_logits(logits, w["k"], x_in.dtype)
-            out = ep_expert_compute(x_in, scores, idx, w1, w2, w["E"], "swiglu")
+            out = ep_expert_compute(x_in, scores, idx, w1, w2, w["E"], "swiglu", context=ep_context)
         out.backward(g_in)
         dx = x_in.grad
         x_in.requires_grad_(False)
@@ -342,7 +346,7 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
             "tflops": flops / (ms * 1e-3) / 1e12,
             "frac_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["burst"],
             "config": {"workload": name, "tokens_per_gpu": w["T"], "hidden": w["d"], "experts": w["E"], "topk": w["k"],
-                       "intermediate": w["I"], "router": w["router"], "parallelism": f"ep{world}" if world > 1 else "single",
+                       "intermediate": w["I"], "router": w["router"], "parallelism": f"ep{world}-{args.ep_mode}" if world > 1 else "single",
                        "l2": "inputs larger than L2 (expert weights are re-read from HBM every step)",
                        "flops_per_step": flops},
             "clocks": clocks,
@@ -497,6 +501,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-mode", default="peer", choices=["peer", "collective"],
+                    help="N > 1: rows over peer-mapped memory inside the kernels (default) or NCCL all-to-all")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")
     ap.add_argument("--device-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for short runs under a profiler)")

@@ -133,6 +133,15 @@ int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src,
                     const int32_t* num_mtiles, void* dst, int64_t padded_rows, int cols,
                     int div, int dtype, void* stream);
 
+/* Expert-parallel dispatch as a pull: dst[p, :] = scale[p] * peer_bases[src_rank[p]][src_row[p], :]
+ * for padded rows p < 128*num_mtiles, zeros where src_rank[p] < 0.  peer_bases is a DEVICE array with
+ * one base pointer per rank of the node (peer-mapped buffers of [*, cols] rows, e.g. symmetric memory);
+ * rows are read with ordinary loads over NVLink.  scale (fp32, may be NULL) is applied in fp32.
+ * No counterpart in the reference (it is single-GPU). */
+int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank,
+                         const int32_t* src_row, const float* scale, const int32_t* num_mtiles,
+                         void* dst, int64_t padded_rows, int cols, int dtype, void* stream);
+
 /* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order. */
 int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows,
                    int cols, int dtype, void* stream);
@@ -145,7 +154,7 @@ int moe_combine_topk(const void* ys, const void* scores, const int32_t* dst_row,
 /* Backward of the combine: for padded row p holding flat position j = (t, s):
  *   gs[p, :]   = scores[j] * dout[t, :]
  *   dscores[j] = dot(dout[t, :], ys[p, :])      (fp32 accumulation, stored in `dtype`)
- * padding rows of gs are zeroed. */
+ * padding rows of gs are zeroed.  gs may be NULL when only dscores is wanted. */
 int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
                     const int32_t* row_src, const int32_t* num_mtiles, void* gs, void* dscores,
                     int64_t num_tokens, int topk, int64_t padded_rows, int cols, int dtype,
@@ -171,6 +180,19 @@ int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act,
                       const int32_t* num_mtiles,
                       int64_t padded_rows, int K, int N, int num_experts, int w_transposed,
                       int act, int dtype, int32_t* status, void* stream);
+
+/* Expert-parallel combine fused into the GEMM: the same contraction as moe_mgrouped_gemm without an
+ * activation, but the epilogue stores accumulator row p at row dest_row[p] of the [*, N] matrix based at
+ * peer_bases[dest_rank[p]] -- the buffer of the GPU that owns the token -- with ordinary stores over
+ * NVLink, tile by tile while the next tile's math runs; rows with dest_rank[p] < 0 are skipped.
+ * peer_bases is a DEVICE array of one base pointer per rank.  The caller synchronises the ranks before
+ * the destination buffers are read.  No counterpart in the reference. */
+int moe_mgrouped_gemm_push(const void* a, const void* w, void* const* peer_bases,
+                           const int32_t* dest_rank, const int32_t* dest_row,
+                           const int32_t* mtile_expert, const int32_t* tile_pairs,
+                           const int32_t* num_mtiles, int64_t padded_rows, int K, int N,
+                           int num_experts, int w_transposed, int dtype, int32_t* status,
+                           void* stream);
 
 /* Backward through the GLU: d_pre[RP, 2N] = dGLU(pre_act[RP, 2N]) * (g[RP, K] @ w[E, N, K]^T),
  * i.e. for the layer: g = score-scaled dOut rows, w = weight2 [E, I, d] (N = I, K = d),

@@ -43,7 +43,7 @@ constexpr int BK = 64;        // K extent of one shared-memory stage: 64 x 2 byt
 constexpr int UMMA_K = 16;    // K extent of one tcgen05.mma for 16-bit inputs
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
-constexpr int kGroupM = 16;   // consecutive row tiles that share a sweep over column tiles (L2 reuse)
+constexpr int kDefaultGroupM = 16;  // consecutive row units that share a sweep over column tiles (L2 reuse)
 constexpr uint32_t kTmemCols = 512;
 
 enum Epilogue : int { EPI_ACT = 0, EPI_GLU = 1, EPI_DGLU = 2 };
@@ -62,7 +62,14 @@ struct GemmArgs {
   void* out;           // EPI_ACT: [rows, N]; EPI_GLU: [rows, N/2]; EPI_DGLU: [rows, 2N]
   void* aux_out;       // EPI_GLU: un-activated product [rows, N] or null
   const void* aux_in;  // EPI_DGLU: saved un-activated product [rows, 2N]
+  // EPI_ACT, M-grouped only: when push_bases != null, accumulator row p is stored at row push_row[p] of the
+  // [*, N] matrix based at push_bases[push_rank[p]] (another GPU's buffer, peer-mapped) instead of `out`;
+  // rows with push_rank[p] < 0 are not stored.
+  void* const* push_bases;
+  const int32_t* push_rank;
+  const int32_t* push_row;
   int32_t act;
+  int32_t group_m;  // row units per scheduling group
   int32_t* status;
 };
 
@@ -122,7 +129,10 @@ struct SmemPlan {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (196608 / kStageBytes) > 8 ? 8 : (196608 / kStageBytes);
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  // plain-store epilogue: each epilogue warp stages 32 rows x 64 columns (128 bytes per row) so that
+  // its global stores cover whole 128-byte row segments
+  static constexpr int kStagingBytes = kEpilogueWarps * 32 * 128;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;  // + alignment slack
 };
 
 // Number of (row unit, column tile) work items and the row-unit / column-tile counts.  A row unit is
@@ -148,11 +158,12 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const Ge
     expert = t / (mt * nt);
     t -= expert * (mt * nt);
   }
-  const int per_group = kGroupM * nt;
+  const int group_m = args.group_m;
+  const int per_group = group_m * nt;
   const int g = t / per_group;
   const int rem = t - g * per_group;
-  const int m_first = g * kGroupM;
-  const int gm = min(kGroupM, mt - m_first);
+  const int m_first = g * group_m;
+  const int gm = min(group_m, mt - m_first);
   const int n_idx = rem / gm;
   const int m_idx = m_first + (rem - n_idx * gm);
   c.n0 = n_idx * BN;
@@ -402,11 +413,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const int row = c.m0 + row_in_tile;
       bool row_ok = c.active;
       long long out_row;  // row index into the output matrix
+      T* row_out = out;  // base of the matrix this lane's row is stored into
       if (KG) {
         row_ok = row_ok && row < args.m_dim;
         out_row = static_cast<long long>(c.expert) * args.m_dim + row;
       } else {
         out_row = row;
+        if (EPI == EPI_ACT && args.push_bases != nullptr) {
+          const int32_t r = row_ok ? __ldg(args.push_rank + row) : -1;
+          row_ok = r >= 0;
+          if (row_ok) {
+            row_out = reinterpret_cast<T*>(args.push_bases[r]);
+            out_row = __ldg(args.push_row + row);
+          }
+        }
       }
       // EPI_DGLU: the saved pre-activation does not depend on the accumulator -- fetch the first
       // chunk's 128 bytes before waiting for the MMAs, then stay one chunk ahead.
@@ -425,6 +445,59 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after();
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
+      if (EPI == EPI_ACT) {
+        // Plain store (optionally with silu/gelu, optionally into another GPU's buffer): two 32-column
+        // chunks at a time go through a swizzled shared-memory tile so that every store instruction
+        // of the warp writes four 128-byte row segments instead of 32 scattered 16-byte pieces.
+        const uint32_t stage_base = tiles_addr + kStages * Plan::kStageBytes + Plan::kBarrierBytes + (warp - 2) * (32 * 128);
+        const unsigned long long my_base = reinterpret_cast<unsigned long long>(row_out + out_row * N);
+#pragma unroll 1
+        for (int chunk = chunk_begin; chunk < chunk_begin + kChunksPerWarp; chunk += 2) {
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            float v[32];
+            if (have_acc) {
+              uint32_t raw[32];
+              tmem_ld_32x32(taddr + (chunk + hc) * 32, raw);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+            }
+            if (args.act == MOE_ACT_SILU) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+            } else if (args.act == MOE_ACT_GELU) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 u = pack8<T>(v + q * 8);
+              const uint32_t addr = stage_base + lane * 128 + (((hc * 4 + q) ^ (lane & 7)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                           : "memory");
+            }
+          }
+          __syncwarp();
+          const int col_pair0 = c.n0 + chunk * 32;  // first of the 64 columns staged
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int r = j * 4 + (lane >> 3);   // row of the warp's 32 this lane writes in this step
+            const int ck = lane & 7;             // 16-byte piece of the row's 128 bytes
+            const unsigned long long base = __shfl_sync(0xFFFFFFFFu, my_base, r);
+            const int ok = __shfl_sync(0xFFFFFFFFu, row_ok ? 1 : 0, r);
+            uint4 u;
+            const uint32_t addr = stage_base + r * 128 + ((ck ^ (r & 7)) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(addr));
+            const int col = col_pair0 + ck * 8;
+            if (ok && col < N) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(base) + col) = u;
+          }
+          __syncwarp();
+        }
+      } else {
 #pragma unroll 1
       for (int chunk = chunk_begin; chunk < chunk_begin + kChunksPerWarp; ++chunk) {
         float v[32];
@@ -463,7 +536,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
             for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
           }
-          T* dst = out + out_row * N + col0;
+          T* dst = row_out + out_row * N + col0;
 #pragma unroll
           for (int q = 0; q < 4; ++q)
             if (col0 + q * 8 < N) *reinterpret_cast<uint4*>(dst + q * 8) = pack8<T>(v + q * 8);
@@ -514,6 +587,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
       }
+      }  // EPI != EPI_ACT
       if (have_acc) {
         // this warp has read its part of the accumulator: one arrival per warp on the leader's barrier
         tc_fence_before();
@@ -639,6 +713,17 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Row units per scheduling group; MOE_SM100_GROUP_M in the environment overrides it (measurement aid).
+static int group_m_setting() {
+  static int cached = 0;
+  if (cached == 0) {
+    const char* v = getenv("MOE_SM100_GROUP_M");
+    const int n = v != nullptr ? atoi(v) : 0;
+    cached = n > 0 ? n : kDefaultGroupM;
+  }
+  return cached;
+}
+
 // CTA pairs are the default; MOE_SM100_SINGLE_CTA=1 in the environment selects the one-CTA kernels
 // (kept for comparison measurements).
 static bool use_cta_pairs() {
@@ -684,11 +769,18 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t padded_rows, 
 
 static int pick_bn(int N) { return (N % 256 == 0 || N % 128 != 0) ? 256 : 128; }
 
+struct PushTarget {
+  void* const* bases = nullptr;
+  const int32_t* rank = nullptr;
+  const int32_t* row = nullptr;
+};
+
 static int mgrouped_common(const void* a, const void* w, void* out, void* aux_out, const void* aux_in,
-                           const int32_t* mtile_expert, const int32_t* tile_pairs, const int32_t* num_mtiles,
+                           const PushTarget& push, const int32_t* mtile_expert, const int32_t* tile_pairs,
+                           const int32_t* num_mtiles,
                            int64_t padded_rows, int K, int N, int E, int w_transposed, int epi, int act, int dtype,
                            int32_t* status, void* stream) {
-  MOE_CHECK_ARG(a && w && out && mtile_expert && num_mtiles, "grouped GEMM: null pointer argument");
+  MOE_CHECK_ARG(a && w && (out || push.bases) && mtile_expert && num_mtiles, "grouped GEMM: null pointer argument");
   MOE_CHECK_ARG(aligned16(a) && aligned16(w) && aligned16(out) && aligned16(aux_out) && aligned16(aux_in),
                 "grouped GEMM: pointers must be 16-byte aligned");
   MOE_CHECK_ARG(padded_rows > 0 && padded_rows % BM == 0, "grouped GEMM: padded_rows=%lld must be a positive multiple of %d",
@@ -709,7 +801,11 @@ static int mgrouped_common(const void* a, const void* w, void* out, void* aux_ou
   args.out = out;
   args.aux_out = aux_out;
   args.aux_in = aux_in;
+  args.push_bases = push.bases;
+  args.push_rank = push.rank;
+  args.push_row = push.row;
   args.act = act;
+  args.group_m = group_m_setting();
   args.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bn = pick_bn(N);
@@ -752,7 +848,7 @@ extern "C" int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* 
                                  void* stream) {
   MOE_CHECK_ARG(act >= MOE_ACT_NONE && act <= MOE_ACT_GEGLU, "moe_mgrouped_gemm: unknown activation %d", act);
   const bool glu = act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU;
-  return mgrouped_common(a, w, out, glu ? pre_act : nullptr, nullptr, mtile_expert, tile_pairs, num_mtiles,
+  return mgrouped_common(a, w, out, glu ? pre_act : nullptr, nullptr, PushTarget{}, mtile_expert, tile_pairs, num_mtiles,
                          padded_rows, K, N, num_experts, w_transposed, glu ? EPI_GLU : EPI_ACT, act, dtype, status,
                          stream);
 }
@@ -763,8 +859,21 @@ extern "C" int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* 
                                       int act, int dtype, int32_t* status, void* stream) {
   MOE_CHECK_ARG(act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU, "moe_mgrouped_gemm_dglu: activation %d is not a GLU", act);
   MOE_CHECK_ARG(pre_act != nullptr, "moe_mgrouped_gemm_dglu: pre_act is null");
-  return mgrouped_common(g, w, d_pre, nullptr, pre_act, mtile_expert, tile_pairs, num_mtiles, padded_rows, K, N,
+  return mgrouped_common(g, w, d_pre, nullptr, pre_act, PushTarget{}, mtile_expert, tile_pairs, num_mtiles, padded_rows, K, N,
                          num_experts, 1, EPI_DGLU, act, dtype, status, stream);
+}
+
+extern "C" int moe_mgrouped_gemm_push(const void* a, const void* w, void* const* peer_bases, const int32_t* dest_rank,
+                                      const int32_t* dest_row, const int32_t* mtile_expert, const int32_t* tile_pairs,
+                                      const int32_t* num_mtiles, int64_t padded_rows, int K, int N, int num_experts,
+                                      int w_transposed, int dtype, int32_t* status, void* stream) {
+  MOE_CHECK_ARG(peer_bases && dest_rank && dest_row, "moe_mgrouped_gemm_push: null pointer argument");
+  PushTarget push;
+  push.bases = peer_bases;
+  push.rank = dest_rank;
+  push.row = dest_row;
+  return mgrouped_common(a, w, nullptr, nullptr, nullptr, push, mtile_expert, tile_pairs, num_mtiles, padded_rows, K, N,
+                         num_experts, w_transposed, EPI_ACT, MOE_ACT_NONE, dtype, status, stream);
 }
 
 extern "C" int moe_kgrouped_gemm(const void* a, const void* b, void* dw, const int32_t* pad_offsets,
@@ -787,6 +896,7 @@ extern "C" int moe_kgrouped_gemm(const void* a, const void* b, void* dw, const i
   args.n_dim = N;
   args.out = dw;
   args.act = MOE_ACT_NONE;
+  args.group_m = group_m_setting();
   args.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int bn = pick_bn(N);

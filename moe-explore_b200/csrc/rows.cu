@@ -28,6 +28,42 @@ gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ ro
   }
 }
 
+// dst[p, :] = scale[p] * bases[src_rank[p]][src_row[p], :], zeros where src_rank[p] < 0.  `bases` holds
+// one base pointer per rank of the node: the source rows live in peers' memory and are read with
+// ordinary 16-byte loads over NVLink (this GPU's own rows through the same path).
+template <typename T>
+__global__ void __launch_bounds__(kRowThreads)
+gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* __restrict__ src_rank,
+                        const int32_t* __restrict__ src_row, const float* __restrict__ scale,
+                        const int32_t* __restrict__ num_mtiles, uint4* __restrict__ dst, int vec_per_row) {
+  const int64_t rows_in_use = static_cast<int64_t>(*num_mtiles) * MOE_TILE_M;
+  for (int64_t p = blockIdx.x; p < rows_in_use; p += gridDim.x) {
+    const int32_t r = src_rank[p];
+    uint4* d = dst + p * vec_per_row;
+    if (r < 0) {
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const uint4* s = bases[r] + static_cast<int64_t>(src_row[p]) * vec_per_row;
+    if (scale == nullptr) {
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = s[v];
+    } else {
+      const float f = scale[p];
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+        const uint4 u = s[v];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 x = Elem<T>::unpack2(w[i]);
+          o[i] = Elem<T>::pack2(f * x.x, f * x.y);
+        }
+        d[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+    }
+  }
+}
+
 // out[j, :] = src[dst_row[j], :]
 __global__ void __launch_bounds__(kRowThreads)
 unpad_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ dst_row, uint4* __restrict__ out,
@@ -86,7 +122,8 @@ combine_bwd_kernel(const uint4* __restrict__ dout, const T* __restrict__ scores,
     const int32_t j = row_src[p];
     uint4* g = gs + p * vec_per_row;
     if (j < 0) {
-      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) g[v] = make_uint4(0, 0, 0, 0);
+      if (gs != nullptr)
+        for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) g[v] = make_uint4(0, 0, 0, 0);
       continue;  // uniform across the CTA
     }
     const float scale = Elem<T>::to_float(scores[j]);
@@ -107,7 +144,7 @@ combine_bwd_kernel(const uint4* __restrict__ dout, const T* __restrict__ scores,
         dot = fmaf(df.y, yf.y, dot);
         ow[i] = Elem<T>::pack2(scale * df.x, scale * df.y);
       }
-      g[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      if (gs != nullptr) g[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
@@ -154,6 +191,27 @@ extern "C" int moe_gather_rows(const void* src, int64_t src_rows, const int32_t*
   return MOE_OK;
 }
 
+extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank, const int32_t* src_row,
+                                    const float* scale, const int32_t* num_mtiles, void* dst, int64_t padded_rows,
+                                    int cols, int dtype, void* stream) {
+  MOE_CHECK_ARG(peer_bases && src_rank && src_row && num_mtiles && dst, "moe_gather_rows_peer: null pointer argument");
+  MOE_CHECK_ARG(aligned16(dst), "moe_gather_rows_peer: dst must be 16-byte aligned");
+  MOE_CHECK_ARG(padded_rows > 0, "moe_gather_rows_peer: bad sizes");
+  MOE_ROW_COMMON_CHECKS("moe_gather_rows_peer", cols, dtype);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = row_grid(padded_rows);
+  const uint4* const* bases = reinterpret_cast<const uint4* const*>(peer_bases);
+  if (dtype == MOE_DTYPE_BF16) {
+    gather_rows_peer_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
+                                                                       static_cast<uint4*>(dst), cols / 8);
+  } else {
+    gather_rows_peer_kernel<__half><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
+                                                                static_cast<uint4*>(dst), cols / 8);
+  }
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}
+
 extern "C" int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows, int cols, int dtype,
                               void* stream) {
   MOE_CHECK_ARG(num_rows >= 0, "moe_unpad_rows: num_rows is negative");
@@ -192,7 +250,7 @@ extern "C" int moe_combine_topk(const void* ys, const void* scores, const int32_
 extern "C" int moe_combine_bwd(const void* dout, const void* scores, const void* ys, const int32_t* row_src,
                                const int32_t* num_mtiles, void* gs, void* dscores, int64_t num_tokens, int topk,
                                int64_t padded_rows, int cols, int dtype, void* stream) {
-  MOE_CHECK_ARG(dout && scores && ys && row_src && num_mtiles && gs && dscores, "moe_combine_bwd: null pointer argument");
+  MOE_CHECK_ARG(dout && scores && ys && row_src && num_mtiles && dscores, "moe_combine_bwd: null pointer argument");
   MOE_CHECK_ARG(aligned16(dout) && aligned16(ys) && aligned16(gs), "moe_combine_bwd: pointers must be 16-byte aligned");
   MOE_CHECK_ARG(num_tokens >= 0 && topk > 0 && padded_rows > 0, "moe_combine_bwd: bad sizes");
   MOE_ROW_COMMON_CHECKS("moe_combine_bwd", cols, dtype);

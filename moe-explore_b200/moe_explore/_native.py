@@ -33,6 +33,8 @@ SIGNATURES = {
     "moe_routing_metadata_static": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 9 + [c_void_p]),
     "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 6 + [c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_void_p]),
+    "moe_mgrouped_gemm_push": (c_int, [c_void_p] * 8 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_combine_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_combine_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
@@ -199,6 +201,31 @@ def gather_rows(src, row_src, num_mtiles, dst, div):
     _count(1)
 
 
+def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst):
+    """dst[p] = scale[p] * peer_bases[src_rank[p]][src_row[p]]; peer_bases: int64 device tensor of base pointers."""
+    require_cuda(peer_bases, dst)
+    with _Timed("rows:gather_peer"):
+        rc = load().moe_gather_rows_peer(_ptr(peer_bases), _ptr(src_rank), _ptr(src_row), _ptr(scale), _ptr(num_mtiles),
+                                         _ptr(dst), dst.size(0), dst.size(1), dtype_code(dst.dtype), _stream())
+    _check("moe_gather_rows_peer", rc)
+    _count(1)
+
+
+def mgrouped_gemm_push(a, w, peer_bases, dest_rank, dest_row, mtile_expert, tile_pairs, num_mtiles, w_transposed,
+                       status=None, rows=None):
+    """Grouped GEMM whose epilogue stores each row into the owning rank's buffer (peer stores)."""
+    require_cuda(a, w, peer_bases)
+    E = w.size(0)
+    K = a.size(1)
+    N = w.size(1) if w_transposed else w.size(2)
+    with _Timed("mgrouped_gemm:push_wt" if w_transposed else "mgrouped_gemm:push", rows):
+        rc = load().moe_mgrouped_gemm_push(_ptr(a), _ptr(w), _ptr(peer_bases), _ptr(dest_rank), _ptr(dest_row),
+                                           _ptr(mtile_expert), _ptr(tile_pairs), _ptr(num_mtiles), a.size(0), K, N, E,
+                                           1 if w_transposed else 0, dtype_code(a.dtype), _ptr(status), _stream())
+    _check("moe_mgrouped_gemm_push", rc)
+    _count(1)
+
+
 def unpad_rows(src, dst_row, out):
     require_cuda(src, out)
     with _Timed("rows:unpad"):
@@ -218,10 +245,10 @@ def combine_topk(ys, scores, dst_row, out, topk):
 
 
 def combine_bwd(dout, scores, ys, row_src, num_mtiles, gs, dscores, topk):
-    require_cuda(dout, ys, gs)
+    require_cuda(dout, ys, dscores)
     with _Timed("rows:combine_bwd"):
         rc = load().moe_combine_bwd(_ptr(dout), _ptr(scores), _ptr(ys), _ptr(row_src), _ptr(num_mtiles), _ptr(gs),
-                                    _ptr(dscores), dout.size(0), topk, gs.size(0), dout.size(1), dtype_code(dout.dtype),
+                                    _ptr(dscores), dout.size(0), topk, ys.size(0), dout.size(1), dtype_code(dout.dtype),
                                     _stream())
     _check("moe_combine_bwd", rc)
     _count(1)

@@ -1,13 +1,24 @@
 """Expert-parallel MoE layer: experts sharded over the ranks of one node, tokens stay data-parallel.
 
 Rank g owns experts [g*E/G, (g+1)*E/G) -- their weights and weight gradients never move.  Per pass
-there is one exchange each way (NCCL all-to-all over NVLink, uneven splits):
+there is one exchange each way:
 
   forward : sort the local (token, slot) rows by global expert (= by owner rank, then by expert)
             -> exchange per-expert counts -> DISPATCH rows to their owners -> local grouped GEMMs
             -> COMBINE rows back -> weighted fold of the top-k slots at the source.
   backward: score-scaled dOut rows are dispatched the same way, the owners run the backward GEMMs
             (expert weight gradients stay local) and dX rows are combined back and folded.
+
+Two data paths implement the exchanges:
+
+  * peer mode (``EPContext``; the fast path): token rows never go through a collective.  Every rank
+    publishes its tokens in a peer-mapped (symmetric-memory) buffer; the expert owners PULL the rows
+    they need straight into the padded expert-sorted layout with the library's gather kernel (loads
+    over NVLink), and the down-projection / dX grouped GEMMs PUSH every output row into the token
+    owner's buffer from their epilogue (stores over NVLink, overlapped with the next tile's math).
+    Only row metadata (8 bytes per routed row) and three tiny barriers go through NCCL.
+  * collective mode: rows are exchanged with ``all_to_all_single`` (NCCL) before and after the local
+    GEMMs; kept as the baseline the peer path is measured against.
 
 The reference has no multi-GPU path; the single-GPU semantics it must reproduce are those of
 topk_moe_forward (reference: src/moe_explore/functional/topk_moe.py:10-64).
@@ -183,18 +194,224 @@ class EPExpertCompute(torch.autograd.Function):
         return dx, d_scores, d_w1, d_w2, None, None, None, None, None
 
 
+# --------------------------------------------------------------------------------------------------
+# peer mode: pull dispatch / push combine over peer-mapped memory
+# --------------------------------------------------------------------------------------------------
+class EPContext:
+    """Peer-mapped buffers of one expert-parallel layer on one rank (created collectively).
+
+    ``src`` [T, d] holds this rank's tokens (forward) or upstream gradient rows (backward) for the
+    expert owners to pull; ``y_back`` / ``dx_back`` [ceil(T*topk/128)*128, d] receive the rows the
+    owners push back, in this rank's expert-sorted order.  A context serves one forward/backward pair
+    at a time: ``y_back`` is read again by the backward pass."""
+
+    def __init__(self, group, num_tokens: int, hidden: int, topk: int, dtype, device, allocate=True):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.num_tokens, self.hidden, self.topk, self.dtype, self.device = num_tokens, hidden, topk, dtype, device
+        self.rows_up = _round_up(max(num_tokens * topk, 1), 128)
+        self.busy = False
+        if allocate:
+            self._allocate_symmetric()
+
+    def _allocate_symmetric(self):
+        import os
+
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer loads/stores only
+        import torch.distributed._symmetric_memory as symm
+
+        def make(rows):
+            t = symm.empty(rows, self.hidden, dtype=self.dtype, device=self.device)
+            handle = symm.rendezvous(t, self.group)
+            ptrs = torch.tensor(list(handle.buffer_ptrs), dtype=torch.int64, device=self.device)
+            return t, handle, ptrs
+
+        self.src, self._h_src, self.src_ptrs = make(self.num_tokens)
+        self.y_back, self._h_y, self.y_ptrs = make(self.rows_up)
+        self.dx_back, self._h_dx, self.dx_ptrs = make(self.rows_up)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+
+@dataclass
+class PeerLayout:
+    """Routing bookkeeping of one step in peer mode (all tensors on the compute device)."""
+    perm32_padded: torch.Tensor   # int32 [rows_up]: flat position of the r-th row in expert order, -1 padding
+    inv_perm32: torch.Tensor      # int32 [R]
+    tiles: torch.Tensor           # int32 [1]: rows_up / 128
+    plan: object                  # local routing plan over the received rows (padded expert-sorted layout)
+    p_rank: torch.Tensor          # int32 [RP]: rank that owns the token of padded row p (-1 padding)
+    p_tok: torch.Tensor           # int32 [RP]: token index on that rank
+    p_dest: torch.Tensor          # int32 [RP]: row of that rank's y_back / dx_back this row is pushed to
+    p_scale: torch.Tensor         # fp32  [RP]: router weight of the row (applied to dOut rows in backward)
+    num_received: int
+
+
+def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: int, group, ops) -> PeerLayout:
+    """Exchange the row metadata of one routing decision: an all-gather of per-expert counts, one host
+    read of the split sizes, and an all-to-all of (token index, router weight) per routed row."""
+    world, me = dist.get_world_size(group), dist.get_rank(group)
+    assert num_experts % world == 0, "experts must divide evenly over the ranks"
+    e_local = num_experts // world
+    topk = indices.size(1)
+    flat = indices.reshape(-1)
+    R, dev = flat.numel(), flat.device
+    perm, counts = ops.sort_by_expert(flat, num_experts)
+    gathered = torch.empty(world * num_experts, dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(gathered, counts.contiguous(), group=group)
+    all_counts = gathered.view(world, num_experts)
+    pair = all_counts.view(world, world, e_local).sum(-1)              # [source, owner] rows
+    host = pair.cpu()
+    send_splits, recv_splits = host[me].tolist(), host[:, me].tolist()
+    num_received = sum(recv_splits)
+    send_base = pair.cumsum(1) - pair                                   # start of each owner's segment at the source
+    base_on_source = send_base[:, me]                                   # [world]
+    recv_counts = pair[:, me]
+    recv_offsets = recv_counts.cumsum(0) - recv_counts
+
+    meta_send = torch.empty(R, 2, dtype=torch.int32, device=dev)
+    meta_send[:, 0] = torch.div(perm, topk, rounding_mode="floor")
+    meta_send[:, 1] = scores.reshape(-1)[perm].float().view(torch.int32)
+    meta_recv = torch.empty(num_received, 2, dtype=torch.int32, device=dev)
+    dist.all_to_all_single(meta_recv, meta_send, output_split_sizes=recv_splits, input_split_sizes=send_splits,
+                           group=group)
+
+    ranks = torch.arange(world, device=dev)
+    src_rank = torch.repeat_interleave(ranks, recv_counts, output_size=num_received)
+    local_ids = torch.arange(e_local, device=dev).repeat(world)
+    local_expert = torch.repeat_interleave(local_ids, all_counts[:, me * e_local:(me + 1) * e_local].reshape(-1),
+                                           output_size=num_received)
+    dest_row = base_on_source[src_rank] + (torch.arange(num_received, device=dev) - recv_offsets[src_rank])
+
+    plan = ops.local_plan(local_expert, e_local)
+    valid = plan.row_src >= 0
+    j = plan.row_src.clamp_min(0).long()
+    if num_received == 0:
+        src_rank = torch.zeros(1, dtype=torch.int64, device=dev)
+        dest_row = torch.zeros(1, dtype=torch.int64, device=dev)
+        meta_recv = torch.zeros(1, 2, dtype=torch.int32, device=dev)
+    minus1 = torch.full((), -1, dtype=torch.int32, device=dev)
+    p_rank = torch.where(valid, src_rank[j].to(torch.int32), minus1)
+    p_tok = torch.where(valid, meta_recv[j, 0], minus1)
+    p_dest = torch.where(valid, dest_row[j].to(torch.int32), minus1)
+    p_scale = torch.where(valid, meta_recv[j, 1].view(torch.float32), torch.zeros((), device=dev))
+
+    inv = torch.empty(R, dtype=torch.int32, device=dev)
+    inv[perm] = torch.arange(R, dtype=torch.int32, device=dev)
+    padded = torch.full((_round_up(max(R, 1), 128),), -1, dtype=torch.int32, device=dev)
+    padded[:R] = perm.to(torch.int32)
+    tiles = torch.full((1,), padded.numel() // 128, dtype=torch.int32, device=dev)
+    return PeerLayout(padded, inv, tiles, plan, p_rank.contiguous(), p_tok.contiguous(), p_dest.contiguous(),
+                      p_scale.contiguous(), num_received)
+
+
+class NativePeerOps(NativeOps):
+    """Peer-mode data path on the library's kernels (CUDA only)."""
+
+    def local_plan(self, local_expert_ids, num_local_experts):
+        return build_routing_plan(local_expert_ids, num_local_experts, 1, want_perm=False)
+
+    def publish(self, ctx: EPContext, rows: torch.Tensor):
+        ctx.src.copy_(rows)
+
+    def barrier(self, ctx: EPContext):
+        """Stream-ordered: every rank's work enqueued so far is complete before any rank continues."""
+        with _native.timed("ep:barrier"):
+            dist.all_reduce(ctx._flag, group=ctx.group)
+
+    def fold_bwd_scores(self, grad_out, scores, y_back, perm32_padded, tiles, topk):
+        dscores = torch.empty_like(scores)
+        _native.combine_bwd(grad_out, scores, y_back, perm32_padded, tiles, None, dscores, topk)
+        return dscores
+
+    def peer_forward(self, ctx: EPContext, lay: PeerLayout, weight1, weight2, act):
+        plan = lay.plan
+        rp, d = plan.padded_rows, ctx.hidden
+        new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
+        xs = new(rp, d)
+        _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, None, plan.num_mtiles, xs)        # dispatch (pull)
+        hidden = new(rp, weight2.size(1))
+        pre_act = new(rp, weight1.size(2))
+        _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False,
+                              act, plan.status, rows=lay.num_received)
+        _native.mgrouped_gemm_push(hidden, weight2, ctx.y_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,             # combine (push)
+                                   plan.tile_pairs, plan.num_mtiles, False, plan.status, rows=lay.num_received)
+        return xs, hidden, pre_act
+
+    def peer_backward(self, ctx: EPContext, lay: PeerLayout, state, weight1, weight2, act):
+        xs, hidden, pre_act = state
+        plan = lay.plan
+        rp, d = plan.padded_rows, ctx.hidden
+        new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
+        gs = new(rp, d)
+        _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, lay.p_scale, plan.num_mtiles, gs)
+        d_pre = new(rp, pre_act.size(1))
+        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, act,
+                                   plan.status, rows=lay.num_received)
+        d_w1 = torch.empty_like(weight1)
+        _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status, rows=lay.num_received, tag="dw1")
+        d_w2 = torch.empty_like(weight2)
+        _native.kgrouped_gemm(hidden, gs, d_w2, plan.pad_offsets, plan.status, rows=lay.num_received, tag="dw2")
+        _native.mgrouped_gemm_push(d_pre, weight1, ctx.dx_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
+                                   plan.tile_pairs, plan.num_mtiles, True, plan.status, rows=lay.num_received)
+        return d_w1, d_w2
+
+
+class PeerEPExpertCompute(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, scores, weight1, weight2, indices, num_experts, act, ep: EPContext, ops):
+        T, topk = x.size(0), indices.size(1)
+        assert T == ep.num_tokens and topk == ep.topk and x.size(1) == ep.hidden, "context was built for another shape"
+        if ep.busy:
+            raise RuntimeError("this EPContext still holds the rows of a forward pass whose backward has not run")
+        scores = scores.to(x.dtype).contiguous()
+        ops.publish(ep, x.contiguous())
+        with _native.timed("ep:layout"):
+            lay = build_peer_layout(indices, scores, num_experts, ep.group, ops)   # its collectives follow the publish
+        state = ops.peer_forward(ep, lay, weight1, weight2, act)
+        ops.barrier(ep)                                                          # every owner has pushed its rows
+        out = ops.fold(ep.y_back, scores, lay.inv_perm32, T, topk)
+        ctx.ep, ctx.ops, ctx.lay, ctx.state, ctx.act = ep, ops, lay, state, act
+        ctx.save_for_backward(scores, weight1, weight2)
+        ep.busy = any(ctx.needs_input_grad)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        scores, weight1, weight2 = ctx.saved_tensors
+        ep, ops, lay = ctx.ep, ctx.ops, ctx.lay
+        T, topk = grad_out.size(0), ep.topk
+        grad_out = grad_out.contiguous()
+        d_scores = ops.fold_bwd_scores(grad_out, scores, ep.y_back, lay.perm32_padded, lay.tiles, topk)
+        ops.publish(ep, grad_out)
+        ops.barrier(ep)                                                          # every rank's dOut is in place
+        d_w1, d_w2 = ops.peer_backward(ep, lay, ctx.state, weight1, weight2, ctx.act)
+        ops.barrier(ep)                                                          # every owner has pushed its dX rows
+        dx = ops.fold(ep.dx_back, None, lay.inv_perm32, T, topk)
+        ep.busy = False
+        return dx, d_scores, d_w1, d_w2, None, None, None, None, None
+
+
 def ep_expert_compute(x: torch.Tensor, scores: torch.Tensor, indices: torch.Tensor, local_weight1: torch.Tensor,
                       local_weight2: torch.Tensor, num_experts: int, act: str = "swiglu", group=None,
-                      ops=None) -> torch.Tensor:
+                      ops=None, context: Optional[EPContext] = None) -> torch.Tensor:
     """Expert-parallel ``out[t] = sum_s scores[t,s] * expert_{indices[t,s]}(x[t])``.
 
     x [T, d] (this rank's tokens), scores [T, k], indices int64 [T, k] with GLOBAL expert ids,
     local_weight1 [E/G, d, 2I], local_weight2 [E/G, I, d] (this rank's experts).  Differentiable with
-    respect to x, scores and the local weights."""
+    respect to x, scores and the local weights.  With ``context`` (an ``EPContext`` built once for the
+    layer) rows move over peer-mapped memory inside the gather kernel and the GEMM epilogues;
+    without it they are exchanged with NCCL all-to-all collectives."""
+    group = group if group is not None else (context.group if context is not None else dist.group.WORLD)
+    if context is not None:
+        if ops is None:
+            _native.require_cuda(x, scores, indices, local_weight1, local_weight2)
+            ops = NativePeerOps()
+        return PeerEPExpertCompute.apply(x, scores, local_weight1.contiguous(), local_weight2.contiguous(), indices,
+                                         num_experts, str(act), context, ops)
     if ops is None:
         _native.require_cuda(x, scores, indices, local_weight1, local_weight2)
         ops = NativeOps()
-    group = group if group is not None else dist.group.WORLD
     with _native.timed("ep:layout"):
         layout = build_dispatch_layout(indices, num_experts, group, ops)
     return EPExpertCompute.apply(x, scores, local_weight1.contiguous(), local_weight2.contiguous(), layout,

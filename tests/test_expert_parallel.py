@@ -53,6 +53,67 @@ class TorchOps:
         return dx, dw1, dw2
 
 
+class TorchPeerOps(TorchOps):
+    """Test double for expert_parallel.NativePeerOps: peer loads / stores are emulated with object
+    all-gathers, the local expert compute is the oracle's."""
+
+    class Plan:
+        pass
+
+    def local_plan(self, local_expert_ids, num_local_experts):
+        po, row_src, dst_row, mte = O.padded_layout(local_expert_ids.view(-1, 1), num_local_experts)
+        plan = self.Plan()
+        plan.row_src, plan.mtile_expert, plan.pad_offsets = row_src, mte, po
+        return plan
+
+    def publish(self, ctx, rows):
+        ctx.src = rows.detach().clone()
+
+    def barrier(self, ctx):
+        dist.barrier(group=ctx.group)
+
+    def fold_bwd_scores(self, grad_out, scores, y_back, perm32_padded, tiles, topk):
+        return self.fold_bwd(grad_out, scores, y_back, perm32_padded, tiles, topk)[1]
+
+    def _pull(self, ctx, lay, scale):
+        everyone = [None] * ctx.world
+        dist.all_gather_object(everyone, ctx.src, group=ctx.group)
+        valid = lay.p_rank >= 0
+        rows = torch.zeros(lay.p_rank.numel(), ctx.hidden, dtype=ctx.src.dtype)
+        for p in torch.nonzero(valid).flatten().tolist():
+            rows[p] = everyone[int(lay.p_rank[p])][int(lay.p_tok[p])]
+        return rows * scale[:, None] if scale is not None else rows
+
+    def _push(self, ctx, lay, rows, target):
+        mine = [(int(lay.p_rank[p]), int(lay.p_dest[p]), rows[p]) for p in torch.nonzero(lay.p_rank >= 0).flatten().tolist()]
+        everyone = [None] * ctx.world
+        dist.all_gather_object(everyone, mine, group=ctx.group)
+        buf = torch.zeros(ctx.rows_up, ctx.hidden, dtype=rows.dtype)
+        for sent in everyone:
+            for rank, row, value in sent:
+                if rank == ctx.rank:
+                    buf[row] = value
+        setattr(ctx, target, buf)
+
+    def _experts(self, lay):
+        return torch.repeat_interleave(lay.plan.mtile_expert.long(), 128)
+
+    def peer_forward(self, ctx, lay, weight1, weight2, act):
+        xs = self._pull(ctx, lay, None)
+        ones = torch.ones(xs.size(0), 1, dtype=xs.dtype)
+        ys = O.expert_compute(xs, ones, self._experts(lay).view(-1, 1), weight1, weight2, act)
+        self._push(ctx, lay, ys, "y_back")
+        return xs
+
+    def peer_backward(self, ctx, lay, xs, weight1, weight2, act):
+        gs = self._pull(ctx, lay, lay.p_scale)
+        ones = torch.ones(xs.size(0), 1, dtype=xs.dtype)
+        with torch.enable_grad():
+            _, dxs, _, dw1, dw2 = O.layer_fwd_bwd(xs, ones, self._experts(lay).view(-1, 1), weight1, weight2, act, gs)
+        self._push(ctx, lay, dxs, "dx_back")
+        return dw1, dw2
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -75,12 +136,12 @@ def _make_problem(world, T, d, E, k, I, skew):
     return w1, w2, per_rank
 
 
-def _ep_worker(rank, world, port, T, d, E, k, I, skew, queue):
+def _ep_worker(rank, world, port, T, d, E, k, I, skew, queue, peer=False):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        from moe_explore.expert_parallel import ep_expert_compute
+        from moe_explore.expert_parallel import EPContext, ep_expert_compute
 
         w1, w2, per_rank = _make_problem(world, T, d, E, k, I, skew)
         e_local = E // world
@@ -89,7 +150,11 @@ def _ep_worker(rank, world, port, T, d, E, k, I, skew, queue):
         scores = scores.clone().requires_grad_()
         lw1 = w1[rank * e_local:(rank + 1) * e_local].clone().requires_grad_()
         lw2 = w2[rank * e_local:(rank + 1) * e_local].clone().requires_grad_()
-        out = ep_expert_compute(x, scores, idx, lw1, lw2, E, "swiglu", ops=TorchOps())
+        if peer:
+            context = EPContext(dist.group.WORLD, T, d, k, x.dtype, x.device, allocate=False)
+            out = ep_expert_compute(x, scores, idx, lw1, lw2, E, "swiglu", ops=TorchPeerOps(), context=context)
+        else:
+            out = ep_expert_compute(x, scores, idx, lw1, lw2, E, "swiglu", ops=TorchOps())
         out.backward(grad)
         queue.put((rank, out.detach(), x.grad, scores.grad, lw1.grad, lw2.grad))
         dist.barrier()
@@ -97,13 +162,14 @@ def _ep_worker(rank, world, port, T, d, E, k, I, skew, queue):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("peer", [False, True], ids=["collective", "peer"])
 @pytest.mark.parametrize("skew", [False, True])
-def test_two_gloo_ranks_match_single_process_oracle(skew):
+def test_two_gloo_ranks_match_single_process_oracle(skew, peer):
     world, T, d, E, k, I = 2, 24, 16, 8, 2, 8
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, T, d, E, k, I, skew, queue)) for r in range(world)]
+    procs = [ctx.Process(target=_ep_worker, args=(r, world, port, T, d, E, k, I, skew, queue, peer)) for r in range(world)]
     for p in procs:
         p.start()
     results = {}
@@ -146,10 +212,15 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(native):
         x, w1, w2, grad = mk(T, d), mk(E, d, 2 * I, std=0.05), mk(E, I, d, std=0.05), mk(T, d)
         top, idx = torch.topk(torch.randn(T, E, generator=g, device="cuda"), k, dim=-1, sorted=False)
         scores = torch.softmax(top, -1).bfloat16()
+        from moe_explore.expert_parallel import EPContext
+
+        context = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, torch.device("cuda", 0))
         outs = []
-        for use_ep in (True, False):
+        for mode in ("peer", "collective", "single"):
             leaves = [t.detach().clone().requires_grad_() for t in (x, scores, w1, w2)]
-            if use_ep:
+            if mode == "peer":
+                out = ep_expert_compute(leaves[0], leaves[1], idx, leaves[2], leaves[3], E, "swiglu", context=context)
+            elif mode == "collective":
                 out = ep_expert_compute(leaves[0], leaves[1], idx, leaves[2], leaves[3], E, "swiglu")
             else:
                 out = expert_compute(leaves[0], leaves[1], leaves[2], leaves[3], build_routing_plan(idx, E, k), "swiglu")
@@ -158,7 +229,8 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(native):
         torch.cuda.synchronize()
         # same kernels on the same rows in the same expert order: forward, dx, dscores identical; weight
         # gradients too (row order inside an expert is the stable order in both paths)
-        for a, b in zip(*outs):
-            assert torch.equal(a, b)
+        for other in outs[:2]:
+            for a, b in zip(other, outs[2]):
+                assert torch.equal(a, b)
     finally:
         dist.destroy_process_group()
