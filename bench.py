@@ -202,8 +202,17 @@ def run_ours(args):
         inp["router_weight"].requires_grad_()
 
     ep_context = None
+    remap = None
     if world > 1:
-        from moe_explore.expert_parallel import EPContext, ep_expert_compute
+        from moe_explore.expert_parallel import EPContext, balanced_placement, ep_expert_compute
+
+        if args.placement == "balanced":
+            # static placement from the measured expert load of this routing (all ranks' tokens)
+            with torch.no_grad():
+                _, idx0 = scores_from_logits(inp["logits"], w["k"], x.dtype)
+                load = torch.bincount(idx0.reshape(-1), minlength=w["E"]).to(torch.int64)
+            dist.all_reduce(load)
+            remap = balanced_placement(load.cpu(), world).to(device)
 
         if args.ep_mode == "peer":
             ep_context = EPContext(dist.group.WORLD, w["T"], w["d"], w["k"], x.dtype, device)
@@ -228,6 +237,8 @@ def run_ours(args):
         else:
             logits = inp["logits"].requires_grad_()
             scores, idx = scores_from_logits(logits, w["k"], x_in.dtype)
+            if remap is not None:
+                idx = remap[idx]   # logical expert id -> position in the sharded weights
             out = ep_expert_compute(x_in, scores, idx, w1, w2, w["E"], "swiglu", context=ep_context)
         out.backward(g_in)
         dx = x_in.grad
@@ -269,13 +280,20 @@ def run_ours(args):
     if not args.device_only:
         e2e_ms = run_e2e(args, step, x, grad_out, sync_all)
 
+    rows_per_rank = None
     if world > 1:
         t = torch.tensor([ms, e2e_ms if e2e_ms is not None else 0.0], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
+        # routed rows each rank's experts received in the timed steps (same routing every step)
+        mine = [r for _, _, r in (profile or {}).get("mgrouped_gemm:glu", [])]
+        rows = torch.tensor([float(sum(mine) / max(len(mine), 1))], device=device)
+        gathered = [torch.zeros_like(rows) for _ in range(world)]
+        dist.all_gather(gathered, rows)
+        rows_per_rank = [int(g.item()) for g in gathered]
 
     if rank == 0:
-        report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router)
+        report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -334,7 +352,7 @@ def run_e2e(args, step, x, grad_out, sync_all):
     return t0.elapsed_time(t1) / args.steps
 
 
-def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router):
+def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank=None):
     if True:
         peaks = measured_peaks()
         tokens = w["T"] * world
@@ -347,6 +365,7 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
             "frac_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["burst"],
             "config": {"workload": name, "tokens_per_gpu": w["T"], "hidden": w["d"], "experts": w["E"], "topk": w["k"],
                        "intermediate": w["I"], "router": w["router"], "parallelism": f"ep{world}-{args.ep_mode}" if world > 1 else "single",
+                       "expert_placement": (args.placement if world > 1 else None),
                        "l2": "inputs larger than L2 (expert weights are re-read from HBM every step)",
                        "flops_per_step": flops},
             "clocks": clocks,
@@ -370,6 +389,10 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
                                 "frac": ach / peaks["sustained"], "peak_source": peaks["source"] + " (sustained)",
                                 "frac_of_burst_peak": ach / peaks["burst"], "avg_launch_ms": avg,
                                 "launches_timed": len(durs), "rows_per_launch": rows_local, "traffic": TRAFFIC_BYTES.get(name)}
+        if rows_per_rank:
+            mean = sum(rows_per_rank) / len(rows_per_rank)
+            line["config"]["routed_rows_per_rank"] = rows_per_rank
+            line["config"]["load_imbalance_max_over_mean"] = round(max(rows_per_rank) / mean, 4) if mean else None
         if profile:
             line["section_ms_per_step"] = {k_: round(sum(a.elapsed_time(b) for a, b, _ in v) / args.steps, 4)
                                            for k_, v in sorted(profile.items())}
@@ -501,6 +524,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
+                    help="N > 1: which experts each rank owns: evened out by measured load (default) or blocks of E/N")
     ap.add_argument("--ep-mode", default="peer", choices=["peer", "collective"],
                     help="N > 1: rows over peer-mapped memory inside the kernels (default) or NCCL all-to-all")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")

@@ -44,6 +44,32 @@ def _round_up(n: int, m: int) -> int:
     return (n + m - 1) // m * m
 
 
+def balanced_placement(expert_load, world: int) -> torch.Tensor:
+    """Static expert placement that evens out the routed rows per rank.
+
+    ``expert_load``: per-expert row counts (any 1-D sequence / tensor of length E, e.g. measured over a
+    few steps).  Every rank still owns exactly E / world experts.  Returns ``remap`` (int64 [E]):
+    ``remap[e]`` is the position of logical expert e in the sharded weight tensors, i.e. rank
+    ``remap[e] // (E / world)`` owns it.  Apply it to the router's indices (``remap[indices]``) and store
+    expert e's weights at position ``remap[e]``.
+
+    Greedy longest-processing-time assignment with a per-rank capacity: experts in decreasing load order,
+    each to the least-loaded rank that still has a free slot."""
+    load = [float(v) for v in (expert_load.tolist() if hasattr(expert_load, "tolist") else expert_load)]
+    num_experts = len(load)
+    assert num_experts % world == 0, "experts must divide evenly over the ranks"
+    cap = num_experts // world
+    total = [0.0] * world
+    used = [0] * world
+    remap = [0] * num_experts
+    for e in sorted(range(num_experts), key=lambda i: (-load[i], i)):
+        r = min((g for g in range(world) if used[g] < cap), key=lambda g: (total[g], g))
+        remap[e] = r * cap + used[r]
+        used[r] += 1
+        total[r] += load[e]
+    return torch.tensor(remap, dtype=torch.int64)
+
+
 class NativeOps:
     """Row movement and local expert compute on the library's CUDA kernels."""
 

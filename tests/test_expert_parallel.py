@@ -196,6 +196,26 @@ def test_two_gloo_ranks_match_single_process_oracle(skew, peer):
         torch.testing.assert_close(results[r][4], dw2_sum[r * e_local:(r + 1) * e_local], rtol=1e-5, atol=1e-6)
 
 
+def test_balanced_placement_is_a_permutation_and_evens_the_load():
+    from moe_explore.expert_parallel import balanced_placement
+
+    g = torch.Generator().manual_seed(3)
+    E, world = 256, 8
+    # top-8 routing with Zipf(1.1) expert popularity (log p + Gumbel noise), as the expert-parallel benchmark draws it
+    p = (torch.arange(1, E + 1, dtype=torch.float64) ** -1.1)[torch.randperm(E, generator=g)]
+    u = torch.rand(8192, E, generator=g, dtype=torch.float64).clamp_min(1e-20)
+    idx = torch.topk(torch.log(p / p.sum()) - torch.log(-torch.log(u)), 8, dim=-1).indices
+    load = torch.bincount(idx.reshape(-1), minlength=E).double()
+    remap = balanced_placement(load, world)
+    assert sorted(remap.tolist()) == list(range(E))
+    per_rank = torch.zeros(world, dtype=torch.float64).index_add(0, remap // (E // world), load)
+    contiguous = load.view(world, -1).sum(1)
+    assert per_rank.max() / per_rank.mean() < 1.08 < contiguous.max() / contiguous.mean()
+    # degenerate inputs: equal loads keep every rank at capacity
+    flat = balanced_placement([1.0] * 16, 4)
+    assert sorted(flat.tolist()) == list(range(16))
+
+
 @pytest.mark.gpu
 def test_single_rank_group_on_native_kernels_equals_single_gpu_path(native):
     from moe_explore.expert_compute import expert_compute
