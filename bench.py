@@ -292,8 +292,20 @@ def run_ours(args):
         dist.all_gather(gathered, rows)
         rows_per_rank = [int(g.item()) for g in gathered]
 
+    cpu_base = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.device_only:
+        cpu_base = cpu_baseline(w, inp, budget_s=20.0)
+    ep_base = None
+    if world == 1 and not args.device_only and not args.no_scaling_base and name == "mixtral_8x7b":
+        # the expert-parallel workload on ONE GPU (all 256 experts local): the denominator for the N > 1 lines
+        del inp, w1, w2, x, grad_out
+        torch.cuda.empty_cache()
+        ep_base = measure_single_gpu(WORKLOADS["deepseek_v3_ep"], device, steps=5)
+        inp = x = None
+
     if rank == 0:
-        report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank)
+        report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank,
+               ep_base, cpu_base)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
@@ -352,7 +364,38 @@ def run_e2e(args, step, x, grad_out, sync_all):
     return t0.elapsed_time(t1) / args.steps
 
 
-def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank=None):
+def measure_single_gpu(w, device, steps):
+    """Device-resident fwd+bwd time of workload ``w`` on this GPU (logit-supplied routing); tokens/s and ms."""
+    from moe_explore.expert_compute import expert_compute
+    from moe_explore.routing_plan import build_routing_plan
+
+    inp = make_inputs(w, device)
+    w1, w2 = inp["w1"].requires_grad_(), inp["w2"].requires_grad_()
+    x, g, logits = inp["x"].requires_grad_(), inp["grad_out"], inp["logits"].requires_grad_()
+
+    def one():
+        scores, idx = scores_from_logits(logits, w["k"], x.dtype)
+        plan = build_routing_plan(idx, w["E"], w["k"], want_perm=False)
+        expert_compute(x, scores, w1, w2, plan, "swiglu").backward(g)
+        x.grad = w1.grad = w2.grad = logits.grad = None
+
+    for _ in range(3):
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        one()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"workload": "deepseek_v3_ep", "n_gpus": 1, "value": w["T"] / (ms * 1e-3), "unit": "tokens/s",
+            "ms_per_step": ms, "tflops": algorithmic_flops(w, w["T"], False) / (ms * 1e-3) / 1e12,
+            "note": "same layer as the N > 1 runs with all experts on one GPU; divide an N-GPU value by N times this"}
+
+
+def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank=None,
+           ep_base=None, cpu_base=None):
     if True:
         peaks = measured_peaks()
         tokens = w["T"] * world
@@ -371,8 +414,8 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
             "clocks": clocks,
             "e2e": None if e2e_ms is None else {
                 "value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": 2 * x.numel() * x.element_size() * world,
-                "d2h_bytes_per_step": 2 * x.numel() * x.element_size() * world},
+                "h2d_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world,
+                "d2h_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world},
             "gpu_launches": launches,
         }
         # roofline of the dominant kernel: the gate/up grouped GEMM (4*R*d*I FLOPs per launch)
@@ -396,14 +439,16 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
         if profile:
             line["section_ms_per_step"] = {k_: round(sum(a.elapsed_time(b) for a, b, _ in v) / args.steps, 4)
                                            for k_, v in sorted(profile.items())}
-        if world == 1 and not args.no_cpu_baseline and not args.device_only:
-            line["cpu_baseline"] = cpu_baseline(w, inp, budget_s=20.0)
+        if cpu_base is not None:
+            line["cpu_baseline"] = cpu_base
+        if ep_base is not None:
+            line["ep_scaling_base"] = ep_base
         print(json.dumps(line), flush=True)
 
 
-# DRAM bytes (read + write) of one launch of the dominant kernel, from the ncu capture summarised
-# under profiles/ (null where no capture has been taken for that workload).
-TRAFFIC_BYTES = {}
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the
+# ncu capture summarised under profiles/ (null where no capture has been taken for that workload).
+TRAFFIC_BYTES = {"mixtral_8x7b": 6.3918e9 + 1.4357e9}
 
 
 # ----------------------------------------------------------------------------------------------
@@ -470,7 +515,11 @@ def run_reference(args):
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     T, d, E, k, I = w["T"], w["d"], w["E"], w["k"], w["I"]
-    # Per-step sample: a token subset against the full-size weights of every expert.
+    # Per-step sample: a token subset against full-size expert weights.  Where all experts' fp32 weights and
+    # gradients would not fit a modest host budget (12 GB of weights), a subset of the experts is used too.
+    e_full = E
+    per_expert_bytes = 3 * d * I * 4
+    E = max(k, min(E, int(12e9 // per_expert_bytes)))
     per_step_budget = 150.0 / (args.steps + args.warmup)
     w1 = torch.empty(E, d, 2 * I)
     w2 = torch.empty(E, I, d)
@@ -502,13 +551,14 @@ def run_reference(args):
         cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
     sec = (time.perf_counter() - t0) / args.steps
     value = t_cpu / sec
-    sample_txt = (f"{t_cpu} of {T} tokens per step, full-size fp32 weights of all {E} experts, oracle forward+backward")
+    sample_txt = (f"{t_cpu} of {T} tokens per step, full-size fp32 weights of {E} of the {e_full} experts "
+                  f"(top-{k} routing among them), oracle forward+backward")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": name, "tokens_per_gpu": T, "hidden": d, "experts": E, "topk": k, "intermediate": I,
-                   "router": w["router"], "sample_tokens_per_step": t_cpu},
+        "config": {"workload": name, "tokens_per_gpu": T, "hidden": d, "experts": e_full, "topk": k, "intermediate": I,
+                   "router": w["router"], "sample_tokens_per_step": t_cpu, "sample_experts": E},
         "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample_txt},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -524,6 +574,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-scaling-base", action="store_true",
+                    help="N = 1: skip the extra measurement of the expert-parallel workload on one GPU")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="N > 1: which experts each rank owns: evened out by measured load (default) or blocks of E/N")
     ap.add_argument("--ep-mode", default="peer", choices=["peer", "collective"],
