@@ -34,6 +34,8 @@ WORKLOADS = {
     "qwen15_moe_a27b": dict(T=16384, d=2048, E=60, k=4, I=1408, router="logits_bias"),
     "deepseek_v3_ep": dict(T=32768, d=7168, E=256, k=8, I=2048, router="zipf"),
     "olmoe_8192": dict(T=8192, d=2048, E=64, k=8, I=1024, router="logits"),
+    # routing-stress sweep on the OLMoE shape: pick T with --tokens and the router with --router
+    "olmoe_sweep": dict(T=8192, d=2048, E=64, k=8, I=1024, router="logits"),
 }
 METRIC = "moe_layer_fwd_bwd_tokens_per_s"
 
@@ -120,11 +122,18 @@ def make_logits(w, T, gen, device, rank=0):
     if w["router"] == "logits_bias":
         bias = torch.randn(E, generator=gen, device=device) * 0.5
         return torch.randn(T, E, generator=gen, device=device) + bias
-    if w["router"] == "zipf":
+    if w["router"] == "degenerate":
+        # >= 90 % of the tokens send a slot to one expert; 8 experts never get a row
+        logits = torch.randn(T, E, generator=gen, device=device)
+        hot = torch.rand(T, generator=gen, device=device) < 0.95
+        logits[hot, 5] += 20.0
+        logits[:, E - 8:] = -1e4
+        return logits
+    if w["router"] in ("zipf", "zipf15"):
         # popularity ~ rank^-1.1 over a random expert permutation (same permutation on every rank);
         # log p + Gumbel noise, so the top-k is a sample without replacement proportional to p
         pg = torch.Generator(device=device).manual_seed(1234)
-        p = torch.arange(1, E + 1, dtype=torch.float32, device=device) ** -1.1
+        p = torch.arange(1, E + 1, dtype=torch.float32, device=device) ** (-1.5 if w["router"] == "zipf15" else -1.1)
         p = (p / p.sum())[torch.randperm(E, generator=pg, device=device)]
         u = torch.rand(T, E, generator=gen, device=device).clamp_min(1e-20)
         return torch.log(p) - torch.log(-torch.log(u))
@@ -193,6 +202,8 @@ def run_ours(args):
     w = dict(WORKLOADS[name])
     if args.tokens:
         w["T"] = args.tokens
+    if args.router:
+        w["router"] = args.router
     inp = make_inputs(w, device, rank, world)
     with_router = inp["router_weight"] is not None
     x, grad_out = inp["x"], inp["grad_out"]
@@ -580,6 +591,8 @@ def main():
                     help="N > 1: which experts each rank owns: evened out by measured load (default) or blocks of E/N")
     ap.add_argument("--ep-mode", default="peer", choices=["peer", "collective"],
                     help="N > 1: rows over peer-mapped memory inside the kernels (default) or NCCL all-to-all")
+    ap.add_argument("--router", default=None, choices=["logits", "logits_bias", "zipf", "zipf15", "degenerate"],
+                    help="override the router distribution of a logit-supplied workload")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")
     ap.add_argument("--device-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for short runs under a profiler)")

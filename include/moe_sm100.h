@@ -137,10 +137,13 @@ int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src,
  * for padded rows p < 128*num_mtiles, zeros where src_rank[p] < 0.  peer_bases is a DEVICE array with
  * one base pointer per rank of the node (peer-mapped buffers of [*, cols] rows, e.g. symmetric memory);
  * rows are read with ordinary loads over NVLink.  scale (fp32, may be NULL) is applied in fp32.
+ * chunk_count > 1 restricts the call to the rows of chunk `chunk_index` of `chunk_count` equal slices of
+ * the tile-pair list (see moe_mgrouped_gemm); num_mtiles is then the int32[2] of moe_routing_metadata.
  * No counterpart in the reference (it is single-GPU). */
 int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank,
                          const int32_t* src_row, const float* scale, const int32_t* num_mtiles,
-                         void* dst, int64_t padded_rows, int cols, int dtype, void* stream);
+                         const int32_t* tile_pairs, int chunk_index, int chunk_count, void* dst,
+                         int64_t padded_rows, int cols, int dtype, void* stream);
 
 /* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order. */
 int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows,
@@ -171,6 +174,9 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
 /* M-grouped: out = epilogue(a[rows of tile] @ w[expert of tile]).
  *   mtile_expert / tile_pairs / num_mtiles come from moe_routing_metadata; tile_pairs may be
  *   NULL, which selects the one-SM-per-tile kernels instead of the paired-SM ones.
+ *   chunk_count > 1 processes only chunk `chunk_index` of `chunk_count` equal slices of the tile-pair list
+ *   (needs tile_pairs): a caller can run the row movement of chunk c+1 on another stream while the GEMMs
+ *   of chunk c run.  chunk_count <= 1 processes everything.
  *   a    [RP, K]
  *   w    [E, K, N] when w_transposed == 0, [E, N, K] when w_transposed == 1
  *   act  MOE_ACT_NONE/SILU/GELU: out [RP, N];  MOE_ACT_SWIGLU/GEGLU: out [RP, N/2] and,
@@ -179,7 +185,8 @@ int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act,
                       const int32_t* mtile_expert, const int32_t* tile_pairs,
                       const int32_t* num_mtiles,
                       int64_t padded_rows, int K, int N, int num_experts, int w_transposed,
-                      int act, int dtype, int32_t* status, void* stream);
+                      int act, int dtype, int chunk_index, int chunk_count, int32_t* status,
+                      void* stream);
 
 /* Expert-parallel combine fused into the GEMM: the same contraction as moe_mgrouped_gemm without an
  * activation, but the epilogue stores accumulator row p at row dest_row[p] of the [*, N] matrix based at
@@ -191,8 +198,8 @@ int moe_mgrouped_gemm_push(const void* a, const void* w, void* const* peer_bases
                            const int32_t* dest_rank, const int32_t* dest_row,
                            const int32_t* mtile_expert, const int32_t* tile_pairs,
                            const int32_t* num_mtiles, int64_t padded_rows, int K, int N,
-                           int num_experts, int w_transposed, int dtype, int32_t* status,
-                           void* stream);
+                           int num_experts, int w_transposed, int dtype, int chunk_index,
+                           int chunk_count, int32_t* status, void* stream);
 
 /* Backward through the GLU: d_pre[RP, 2N] = dGLU(pre_act[RP, 2N]) * (g[RP, K] @ w[E, N, K]^T),
  * i.e. for the layer: g = score-scaled dOut rows, w = weight2 [E, I, d] (N = I, K = d),
@@ -202,7 +209,8 @@ int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, vo
                            const int32_t* mtile_expert, const int32_t* tile_pairs,
                            const int32_t* num_mtiles,
                            int64_t padded_rows, int K, int N, int num_experts, int act,
-                           int dtype, int32_t* status, void* stream);
+                           int dtype, int chunk_index, int chunk_count, int32_t* status,
+                           void* stream);
 
 /* K-grouped (expert weight gradients): dw[e] = a[rows of e]^T @ b[rows of e],
  *   a [RP, M], b [RP, N], dw [E, M, N]; experts without rows get zeros.

@@ -69,6 +69,8 @@ struct GemmArgs {
   const int32_t* push_rank;
   const int32_t* push_row;
   int32_t act;
+  int32_t chunk_index;  // M-grouped: process only chunk `chunk_index` of `chunk_count` equal slices of the tile
+  int32_t chunk_count;  // pairs (lets a caller pipeline row movement against the GEMM); count <= 1 = everything
   int32_t group_m;  // row units per scheduling group
   int32_t hint_weights_stream;  // 1: weight tiles get the evict-first L2 policy
   int32_t* status;
@@ -139,20 +141,36 @@ struct SmemPlan {
 // Number of (row unit, column tile) work items and the row-unit / column-tile counts.  A row unit is
 // one 128-row tile (one CTA) or a pair of them (CTA pair).
 template <bool KG, int CTAS>
-__device__ __forceinline__ int total_tiles(const GemmArgs& args, int& mt, int& nt, int BN) {
+__device__ __forceinline__ int total_tiles(const GemmArgs& args, int& mt, int& nt, int& m_begin, int BN) {
   nt = (args.n_dim + BN - 1) / BN;
+  m_begin = 0;
   if (KG) {
     mt = (args.m_dim + BM * CTAS - 1) / (BM * CTAS);
     return args.num_experts * mt * nt;
   }
   mt = args.num_mtiles[CTAS - 1];
+  if (args.chunk_count > 1) {
+    // chunks are equal slices of the PAIR list; the one-CTA kernels translate pair bounds to tile bounds
+    const int pairs = args.num_mtiles[1];
+    const int p0 = static_cast<int>(static_cast<long long>(pairs) * args.chunk_index / args.chunk_count);
+    const int p1 = static_cast<int>(static_cast<long long>(pairs) * (args.chunk_index + 1) / args.chunk_count);
+    if (CTAS == 2) {
+      m_begin = p0;
+      mt = p1 - p0;
+    } else {
+      m_begin = p0 < pairs ? (args.tile_pairs[p0] & 0xFFFFF) : mt;
+      const int t1 = p1 < pairs ? (args.tile_pairs[p1] & 0xFFFFF) : mt;
+      mt = t1 - m_begin;
+    }
+  }
   return mt * nt;
 }
 
 // Row units are walked in groups of kGroupM: inside a group every column tile is visited for all
 // rows of the group before moving on, so concurrently running CTAs share operand tiles in L2.
 template <bool KG, int CTAS>
-__device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const GemmArgs& args, int BN, int rank) {
+__device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, int m_begin, const GemmArgs& args, int BN,
+                                                 int rank) {
   TileCoord c;
   int expert = 0;
   if (KG) {
@@ -166,7 +184,7 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const Ge
   const int m_first = g * group_m;
   const int gm = min(group_m, mt - m_first);
   const int n_idx = rem / gm;
-  const int m_idx = m_first + (rem - n_idx * gm);
+  const int m_idx = m_begin + m_first + (rem - n_idx * gm);
   c.n0 = n_idx * BN;
   c.active = true;
   if (KG) {
@@ -259,8 +277,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  int mt, nt;
-  const int ntiles = total_tiles<KG, CTAS>(args, mt, nt, BN);
+  int mt, nt, m_begin;
+  const int ntiles = total_tiles<KG, CTAS>(args, mt, nt, m_begin, BN);
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
@@ -276,11 +294,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const bool hinted = !KG && args.hint_weights_stream != 0;
       const uint64_t pol_a = hinted ? l2_policy_evict_last() : l2_policy_evict_normal();
       const uint64_t pol_b = hinted ? l2_policy_evict_first() : l2_policy_evict_normal();
-      TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, args, BN, rank);
+      TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, m_begin, args, BN, rank);
       for (int t = unit; t < ntiles && ok; t += num_units) {
         const TileCoord c = c_next;
         // fetch the next work item's coordinates now; the loads complete while this tile streams
-        if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, args, BN, rank);
+        if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, m_begin, args, BN, rank);
         for (int kb = 0; kb < c.kiters; ++kb) {
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, args.status, DS_TIMEOUT_PRODUCER)) {
             ok = false;
@@ -348,10 +366,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
-      TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, args, BN, rank);
+      TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, m_begin, args, BN, rank);
       for (int t = unit; t < ntiles && ok; t += num_units) {
         const TileCoord c = c_next;
-        if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, args, BN, rank);
+        if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, m_begin, args, BN, rank);
         if (c.kiters == 0) continue;  // empty expert: the epilogue writes zeros on its own
         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, args.status, DS_TIMEOUT_MMA)) break;
         tc_fence_after();
@@ -413,10 +431,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     const T* aux_in = reinterpret_cast<const T*>(args.aux_in);
     const int N = args.n_dim;
     const uint32_t tempty_leader = kPair ? mapa_shared(tempty_bar, 0) : tempty_bar;
-    TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, args, BN, rank);
+    TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, m_begin, args, BN, rank);
     for (int t = unit; t < ntiles; t += num_units) {
       const TileCoord c = c_next;
-      if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, args, BN, rank);
+      if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, m_begin, args, BN, rank);
       const bool have_acc = c.kiters != 0;
       const int row = c.m0 + row_in_tile;
       bool row_ok = c.active;
@@ -783,9 +801,14 @@ struct PushTarget {
   const int32_t* row = nullptr;
 };
 
+struct Chunk {
+  int index = 0;
+  int count = 1;
+};
+
 static int mgrouped_common(const void* a, const void* w, void* out, void* aux_out, const void* aux_in,
-                           const PushTarget& push, const int32_t* mtile_expert, const int32_t* tile_pairs,
-                           const int32_t* num_mtiles,
+                           const PushTarget& push, const Chunk& chunk, const int32_t* mtile_expert,
+                           const int32_t* tile_pairs, const int32_t* num_mtiles,
                            int64_t padded_rows, int K, int N, int E, int w_transposed, int epi, int act, int dtype,
                            int32_t* status, void* stream) {
   MOE_CHECK_ARG(a && w && (out || push.bases) && mtile_expert && num_mtiles, "grouped GEMM: null pointer argument");
@@ -799,7 +822,11 @@ static int mgrouped_common(const void* a, const void* w, void* out, void* aux_ou
     return MOE_ERR_UNSUPPORTED;
   }
   MOE_CHECK_ARG(dtype == MOE_DTYPE_BF16 || dtype == MOE_DTYPE_F16, "grouped GEMM: unknown dtype %d", dtype);
+  MOE_CHECK_ARG(chunk.count <= 1 || (tile_pairs != nullptr && chunk.index >= 0 && chunk.index < chunk.count),
+                "grouped GEMM: chunk %d of %d needs tile_pairs and 0 <= index < count", chunk.index, chunk.count);
   GemmArgs args{};
+  args.chunk_index = chunk.index;
+  args.chunk_count = chunk.count;
   args.mtile_expert = mtile_expert;
   args.tile_pairs = tile_pairs;
   args.num_mtiles = num_mtiles;
@@ -853,11 +880,12 @@ using namespace moe;
 
 extern "C" int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act, const int32_t* mtile_expert,
                                  const int32_t* tile_pairs, const int32_t* num_mtiles, int64_t padded_rows, int K,
-                                 int N, int num_experts, int w_transposed, int act, int dtype, int32_t* status,
-                                 void* stream) {
+                                 int N, int num_experts, int w_transposed, int act, int dtype, int chunk_index,
+                                 int chunk_count, int32_t* status, void* stream) {
   MOE_CHECK_ARG(act >= MOE_ACT_NONE && act <= MOE_ACT_GEGLU, "moe_mgrouped_gemm: unknown activation %d", act);
   const bool glu = act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU;
-  return mgrouped_common(a, w, out, glu ? pre_act : nullptr, nullptr, PushTarget{}, mtile_expert, tile_pairs, num_mtiles,
+  return mgrouped_common(a, w, out, glu ? pre_act : nullptr, nullptr, PushTarget{}, Chunk{chunk_index, chunk_count},
+                         mtile_expert, tile_pairs, num_mtiles,
                          padded_rows, K, N, num_experts, w_transposed, glu ? EPI_GLU : EPI_ACT, act, dtype, status,
                          stream);
 }
@@ -865,23 +893,27 @@ extern "C" int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* 
 extern "C" int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, void* d_pre,
                                       const int32_t* mtile_expert, const int32_t* tile_pairs,
                                       const int32_t* num_mtiles, int64_t padded_rows, int K, int N, int num_experts,
-                                      int act, int dtype, int32_t* status, void* stream) {
+                                      int act, int dtype, int chunk_index, int chunk_count, int32_t* status,
+                                      void* stream) {
   MOE_CHECK_ARG(act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU, "moe_mgrouped_gemm_dglu: activation %d is not a GLU", act);
   MOE_CHECK_ARG(pre_act != nullptr, "moe_mgrouped_gemm_dglu: pre_act is null");
-  return mgrouped_common(g, w, d_pre, nullptr, pre_act, PushTarget{}, mtile_expert, tile_pairs, num_mtiles, padded_rows, K, N,
+  return mgrouped_common(g, w, d_pre, nullptr, pre_act, PushTarget{}, Chunk{chunk_index, chunk_count}, mtile_expert,
+                         tile_pairs, num_mtiles, padded_rows, K, N,
                          num_experts, 1, EPI_DGLU, act, dtype, status, stream);
 }
 
 extern "C" int moe_mgrouped_gemm_push(const void* a, const void* w, void* const* peer_bases, const int32_t* dest_rank,
                                       const int32_t* dest_row, const int32_t* mtile_expert, const int32_t* tile_pairs,
                                       const int32_t* num_mtiles, int64_t padded_rows, int K, int N, int num_experts,
-                                      int w_transposed, int dtype, int32_t* status, void* stream) {
+                                      int w_transposed, int dtype, int chunk_index, int chunk_count, int32_t* status,
+                                      void* stream) {
   MOE_CHECK_ARG(peer_bases && dest_rank && dest_row, "moe_mgrouped_gemm_push: null pointer argument");
   PushTarget push;
   push.bases = peer_bases;
   push.rank = dest_rank;
   push.row = dest_row;
-  return mgrouped_common(a, w, nullptr, nullptr, nullptr, push, mtile_expert, tile_pairs, num_mtiles, padded_rows, K, N,
+  return mgrouped_common(a, w, nullptr, nullptr, nullptr, push, Chunk{chunk_index, chunk_count}, mtile_expert, tile_pairs,
+                         num_mtiles, padded_rows, K, N,
                          num_experts, w_transposed, EPI_ACT, MOE_ACT_NONE, dtype, status, stream);
 }
 

@@ -33,13 +33,13 @@ SIGNATURES = {
     "moe_routing_metadata_static": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 9 + [c_void_p]),
     "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 6 + [c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
-    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_int, c_void_p]),
-    "moe_mgrouped_gemm_push": (c_int, [c_void_p] * 8 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "moe_mgrouped_gemm_push": (c_int, [c_void_p] * 8 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_combine_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_combine_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
-    "moe_mgrouped_gemm": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
-    "moe_mgrouped_gemm_dglu": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moe_mgrouped_gemm": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moe_mgrouped_gemm_dglu": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_kgrouped_gemm": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
 }
 
@@ -201,18 +201,19 @@ def gather_rows(src, row_src, num_mtiles, dst, div):
     _count(1)
 
 
-def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst):
+def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst, tile_pairs=None, chunk=(0, 1)):
     """dst[p] = scale[p] * peer_bases[src_rank[p]][src_row[p]]; peer_bases: int64 device tensor of base pointers."""
     require_cuda(peer_bases, dst)
     with _Timed("rows:gather_peer"):
         rc = load().moe_gather_rows_peer(_ptr(peer_bases), _ptr(src_rank), _ptr(src_row), _ptr(scale), _ptr(num_mtiles),
-                                         _ptr(dst), dst.size(0), dst.size(1), dtype_code(dst.dtype), _stream())
+                                         _ptr(tile_pairs), chunk[0], chunk[1], _ptr(dst), dst.size(0), dst.size(1),
+                                         dtype_code(dst.dtype), _stream())
     _check("moe_gather_rows_peer", rc)
     _count(1)
 
 
 def mgrouped_gemm_push(a, w, peer_bases, dest_rank, dest_row, mtile_expert, tile_pairs, num_mtiles, w_transposed,
-                       status=None, rows=None):
+                       status=None, rows=None, chunk=(0, 1)):
     """Grouped GEMM whose epilogue stores each row into the owning rank's buffer (peer stores)."""
     require_cuda(a, w, peer_bases)
     E = w.size(0)
@@ -221,7 +222,8 @@ def mgrouped_gemm_push(a, w, peer_bases, dest_rank, dest_row, mtile_expert, tile
     with _Timed("mgrouped_gemm:push_wt" if w_transposed else "mgrouped_gemm:push", rows):
         rc = load().moe_mgrouped_gemm_push(_ptr(a), _ptr(w), _ptr(peer_bases), _ptr(dest_rank), _ptr(dest_row),
                                            _ptr(mtile_expert), _ptr(tile_pairs), _ptr(num_mtiles), a.size(0), K, N, E,
-                                           1 if w_transposed else 0, dtype_code(a.dtype), _ptr(status), _stream())
+                                           1 if w_transposed else 0, dtype_code(a.dtype), chunk[0], chunk[1],
+                                           _ptr(status), _stream())
     _check("moe_mgrouped_gemm_push", rc)
     _count(1)
 
@@ -254,7 +256,8 @@ def combine_bwd(dout, scores, ys, row_src, num_mtiles, gs, dscores, topk):
     _count(1)
 
 
-def mgrouped_gemm(a, w, out, pre_act, mtile_expert, tile_pairs, num_mtiles, w_transposed, act, status=None, rows=None):
+def mgrouped_gemm(a, w, out, pre_act, mtile_expert, tile_pairs, num_mtiles, w_transposed, act, status=None, rows=None,
+                  chunk=(0, 1)):
     require_cuda(a, w, out)
     E = w.size(0)
     K = a.size(1)
@@ -263,18 +266,19 @@ def mgrouped_gemm(a, w, out, pre_act, mtile_expert, tile_pairs, num_mtiles, w_tr
     with _Timed(key, rows):
         rc = load().moe_mgrouped_gemm(_ptr(a), _ptr(w), _ptr(out), _ptr(pre_act), _ptr(mtile_expert),
                                       _ptr(tile_pairs), _ptr(num_mtiles), a.size(0), K, N, E, 1 if w_transposed else 0, ACT_CODES[act],
-                                      dtype_code(a.dtype), _ptr(status), _stream())
+                                      dtype_code(a.dtype), chunk[0], chunk[1], _ptr(status), _stream())
     _check("moe_mgrouped_gemm", rc)
     _count(1)
 
 
-def mgrouped_gemm_dglu(g, w, pre_act, d_pre, mtile_expert, tile_pairs, num_mtiles, act, status=None, rows=None):
+def mgrouped_gemm_dglu(g, w, pre_act, d_pre, mtile_expert, tile_pairs, num_mtiles, act, status=None, rows=None,
+                       chunk=(0, 1)):
     require_cuda(g, w, pre_act, d_pre)
     E, N, K = w.shape
     with _Timed("mgrouped_gemm:dglu", rows):
         rc = load().moe_mgrouped_gemm_dglu(_ptr(g), _ptr(w), _ptr(pre_act), _ptr(d_pre), _ptr(mtile_expert),
                                            _ptr(tile_pairs), _ptr(num_mtiles), g.size(0), K, N, E, ACT_CODES[act], dtype_code(g.dtype),
-                                           _ptr(status), _stream())
+                                           chunk[0], chunk[1], _ptr(status), _stream())
     _check("moe_mgrouped_gemm_dglu", rc)
     _count(1)
 

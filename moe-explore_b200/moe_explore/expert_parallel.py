@@ -238,6 +238,8 @@ class EPContext:
         self.num_tokens, self.hidden, self.topk, self.dtype, self.device = num_tokens, hidden, topk, dtype, device
         self.rows_up = _round_up(max(num_tokens * topk, 1), 128)
         self.busy = False
+        self.chunks = 4          # slices of the local rows pipelined between the pull and the GEMMs
+        self.comm_stream = None  # side stream the pulls run on (created with the buffers)
         if allocate:
             self._allocate_symmetric()
 
@@ -257,6 +259,7 @@ class EPContext:
         self.y_back, self._h_y, self.y_ptrs = make(self.rows_up)
         self.dx_back, self._h_dx, self.dx_ptrs = make(self.rows_up)
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.comm_stream = torch.cuda.Stream(device=self.device)
 
 
 @dataclass
@@ -350,36 +353,58 @@ class NativePeerOps(NativeOps):
         _native.combine_bwd(grad_out, scores, y_back, perm32_padded, tiles, None, dscores, topk)
         return dscores
 
+    def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
+        """Enqueue the pull of every chunk on the side stream; returns one event per chunk."""
+        plan, chunks = lay.plan, max(1, ctx.chunks)
+        main = torch.cuda.current_stream()
+        ctx.comm_stream.wait_stream(main)          # the layout arrays and the destination exist
+        events = []
+        with torch.cuda.stream(ctx.comm_stream):
+            for c in range(chunks):
+                _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, scale, plan.num_mtiles, dst,
+                                         plan.tile_pairs, (c, chunks))
+                ev = torch.cuda.Event()
+                ev.record(ctx.comm_stream)
+                events.append(ev)
+        return events
+
     def peer_forward(self, ctx: EPContext, lay: PeerLayout, weight1, weight2, act):
-        plan = lay.plan
+        """Dispatch (pull) chunk c+1 on the side stream while the gate/up and down GEMMs of chunk c run; the
+        down GEMM's epilogue pushes its rows to the token owners (combine)."""
+        plan, chunks = lay.plan, max(1, ctx.chunks)
         rp, d = plan.padded_rows, ctx.hidden
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
-        xs = new(rp, d)
-        _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, None, plan.num_mtiles, xs)        # dispatch (pull)
-        hidden = new(rp, weight2.size(1))
-        pre_act = new(rp, weight1.size(2))
-        _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False,
-                              act, plan.status, rows=lay.num_received)
-        _native.mgrouped_gemm_push(hidden, weight2, ctx.y_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,             # combine (push)
-                                   plan.tile_pairs, plan.num_mtiles, False, plan.status, rows=lay.num_received)
+        xs, hidden, pre_act = new(rp, d), new(rp, weight2.size(1)), new(rp, weight1.size(2))
+        main = torch.cuda.current_stream()
+        events = self._pull_chunks(ctx, lay, None, xs)
+        for c in range(chunks):
+            main.wait_event(events[c])
+            _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
+                                  False, act, plan.status, rows=lay.num_received / chunks, chunk=(c, chunks))
+            _native.mgrouped_gemm_push(hidden, weight2, ctx.y_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
+                                       plan.tile_pairs, plan.num_mtiles, False, plan.status,
+                                       rows=lay.num_received / chunks, chunk=(c, chunks))
         return xs, hidden, pre_act
 
     def peer_backward(self, ctx: EPContext, lay: PeerLayout, state, weight1, weight2, act):
         xs, hidden, pre_act = state
-        plan = lay.plan
+        plan, chunks = lay.plan, max(1, ctx.chunks)
         rp, d = plan.padded_rows, ctx.hidden
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
-        gs = new(rp, d)
-        _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, lay.p_scale, plan.num_mtiles, gs)
-        d_pre = new(rp, pre_act.size(1))
-        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, act,
-                                   plan.status, rows=lay.num_received)
+        gs, d_pre = new(rp, d), new(rp, pre_act.size(1))
+        main = torch.cuda.current_stream()
+        events = self._pull_chunks(ctx, lay, lay.p_scale, gs)      # score-scaled dOut rows
+        for c in range(chunks):
+            main.wait_event(events[c])
+            _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
+                                       act, plan.status, rows=lay.num_received / chunks, chunk=(c, chunks))
+            _native.mgrouped_gemm_push(d_pre, weight1, ctx.dx_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
+                                       plan.tile_pairs, plan.num_mtiles, True, plan.status,
+                                       rows=lay.num_received / chunks, chunk=(c, chunks))
         d_w1 = torch.empty_like(weight1)
         _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status, rows=lay.num_received, tag="dw1")
         d_w2 = torch.empty_like(weight2)
         _native.kgrouped_gemm(hidden, gs, d_w2, plan.pad_offsets, plan.status, rows=lay.num_received, tag="dw2")
-        _native.mgrouped_gemm_push(d_pre, weight1, ctx.dx_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
-                                   plan.tile_pairs, plan.num_mtiles, True, plan.status, rows=lay.num_received)
         return d_w1, d_w2
 
 

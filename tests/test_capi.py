@@ -42,7 +42,7 @@ def test_size_helpers(native):
 
 def test_invalid_arguments_are_reported_not_launched(native):
     lib = native.load()
-    rc = lib.moe_mgrouped_gemm(None, None, None, None, None, None, None, 128, 64, 64, 1, 0, 0, 0, None, None)
+    rc = lib.moe_mgrouped_gemm(None, None, None, None, None, None, None, 128, 64, 64, 1, 0, 0, 0, 0, 1, None, None)
     assert rc == -1 and b"null" in lib.moe_last_error()
     rc = lib.moe_routing_metadata(None, -5, 8, None, None, None, None, None, None, None, None, None, None, 0, None)
     assert rc == -1 and b"negative" in lib.moe_last_error()
@@ -52,12 +52,14 @@ def test_invalid_arguments_are_reported_not_launched(native):
     p = ctypes.addressof(buf)
     p += (-p) % 16  # the library checks 16-byte alignment before anything else
     # K not a multiple of 8 (the reference's K=300, N=20 test shape): unsupported, stated clearly
-    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 300, 20, 2, 0, 0, 0, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 300, 20, 2, 0, 0, 0, 0, 1, None, None)
     assert rc == -2 and b"multiples of 8" in lib.moe_last_error()
-    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 100, 64, 64, 2, 0, 0, 0, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 100, 64, 64, 2, 0, 0, 0, 0, 1, None, None)
     assert rc == -1 and b"padded_rows" in lib.moe_last_error()
-    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 64, 64, 2, 0, 9, 0, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 64, 64, 2, 0, 9, 0, 0, 1, None, None)
     assert rc == -1 and b"activation" in lib.moe_last_error()
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, None, p, 128, 64, 64, 2, 0, 0, 0, 1, 4, None, None)
+    assert rc == -1 and b"chunk" in lib.moe_last_error()   # chunked launches need the tile-pair list
     rc = lib.moe_kgrouped_gemm(p, p, p, p, 128, 64, 60, 2, 0, None, None)
     assert rc == -2
     rc = lib.moe_combine_topk(p, None, p, p, 4, 0, 64, 0, None)

@@ -166,3 +166,28 @@ def test_kgrouped_weight_gradient_gemm(E, M, N, rows, native):
     for e in range(E):
         if counts[e] == 0:
             assert int(dw[e].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("chunks", [2, 3, 7])
+def test_chunked_launches_cover_every_tile_exactly_once(chunks, native):
+    """A grouped GEMM run as `chunks` launches over slices of the tile-pair list equals one launch, bit for bit."""
+    from moe_explore.routing_plan import build_routing_plan
+
+    g = torch.Generator().manual_seed(chunks)
+    E, T, K, N = 6, 1500, 256, 512
+    idx = torch.randint(0, E, (T, 1), generator=g)
+    plan = build_routing_plan(idx.cuda(), E, 1)
+    a = torch.randn(plan.padded_rows, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(E, K, N, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    whole = torch.zeros(plan.padded_rows, N // 2, dtype=torch.bfloat16, device="cuda")
+    pre_whole = torch.zeros(plan.padded_rows, N, dtype=torch.bfloat16, device="cuda")
+    native.mgrouped_gemm(a, w, whole, pre_whole, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, "swiglu",
+                         plan.status)
+    parts = torch.zeros_like(whole)
+    pre_parts = torch.zeros_like(pre_whole)
+    for c in range(chunks):
+        native.mgrouped_gemm(a, w, parts, pre_parts, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, "swiglu",
+                             plan.status, chunk=(c, chunks))
+    plan.check()
+    n = int(plan.num_mtiles[0].item()) * 128
+    assert torch.equal(parts[:n], whole[:n]) and torch.equal(pre_parts[:n], pre_whole[:n])
