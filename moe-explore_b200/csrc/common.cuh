@@ -284,6 +284,13 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// 16-byte global store with the streaming (evict-first) cache policy: GEMM outputs are written once and
+// not re-read by the kernel that writes them, so they should not displace operand tiles in L2.
+__device__ __forceinline__ void st_global_stream(void* ptr, const uint4& v) {
+  asm volatile("st.global.cs.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
 // Activation math (fp32).
 __device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoidf_fast(x); }

@@ -74,6 +74,9 @@ struct GemmArgs {
   int32_t group_m;  // row units per scheduling group
   int32_t hint_weights_stream;  // 1: weight tiles get the evict-first L2 policy
   int32_t* status;
+#ifdef MOE_GEMM_STATS
+  long long* stats;  // [grid][4]: MMA thread cycles {total, waiting for operands, waiting for a free accumulator, tiles}
+#endif
 };
 
 struct TileCoord {
@@ -366,19 +369,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+#ifdef MOE_GEMM_STATS
+      long long st_total = clock64(), st_full = 0, st_acc = 0, st_tiles = 0;
+#endif
       TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, m_begin, args, BN, rank);
       for (int t = unit; t < ntiles && ok; t += num_units) {
         const TileCoord c = c_next;
         if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, m_begin, args, BN, rank);
         if (c.kiters == 0) continue;  // empty expert: the epilogue writes zeros on its own
+#ifdef MOE_GEMM_STATS
+        const long long t_acc0 = clock64();
+#endif
         if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, args.status, DS_TIMEOUT_MMA)) break;
+#ifdef MOE_GEMM_STATS
+        st_acc += clock64() - t_acc0;
+        ++st_tiles;
+#endif
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < c.kiters; ++kb) {
+#ifdef MOE_GEMM_STATS
+          const long long t_full0 = clock64();
+#endif
           if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, DS_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
+#ifdef MOE_GEMM_STATS
+          st_full += clock64() - t_full0;
+#endif
           tc_fence_after();
           const uint32_t sa = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t sb = sa + Plan::kABytes;
@@ -415,6 +434,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       if (!ok || *abort_flag) {
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
+#ifdef MOE_GEMM_STATS
+      if (args.stats != nullptr) {
+        long long* o = args.stats + 4 * blockIdx.x;
+        o[0] = clock64() - st_total;
+        o[1] = st_full;
+        o[2] = st_acc;
+        o[3] = st_tiles;
+      }
+#endif
     }
   } else {
     // ------------------------------ epilogue ----------------------------------
@@ -839,6 +867,12 @@ static int mgrouped_common(const void* a, const void* w, void* out, void* aux_ou
   args.push_bases = push.bases;
   args.push_rank = push.rank;
   args.push_row = push.row;
+#ifdef MOE_GEMM_STATS
+  {
+    const char* sp = getenv("MOE_GEMM_STATS_PTR");
+    args.stats = sp != nullptr ? reinterpret_cast<long long*>(strtoull(sp, nullptr, 0)) : nullptr;
+  }
+#endif
   args.act = act;
   args.group_m = group_m_setting();
   args.hint_weights_stream = getenv("MOE_SM100_L2_HINT") != nullptr ? 1 : 0;

@@ -13,7 +13,8 @@ from ctypes import c_int, c_int32, c_int64, c_size_t, c_void_p, c_char_p, POINTE
 import torch
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(os.path.dirname(_PKG_DIR), "libmoe_sm100.so")
+# MOE_SM100_LIBRARY points at another build of the same library (e.g. one compiled with instrumentation)
+LIB_PATH = os.environ.get("MOE_SM100_LIBRARY") or os.path.join(os.path.dirname(_PKG_DIR), "libmoe_sm100.so")
 
 MOE_DTYPE_BF16 = 0
 MOE_DTYPE_F16 = 1

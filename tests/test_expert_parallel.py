@@ -254,3 +254,94 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(native):
                 assert torch.equal(a, b)
     finally:
         dist.destroy_process_group()
+
+
+def _gpu_ep_worker(rank, world, port, queue):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from moe_explore.expert_parallel import EPContext, balanced_placement, ep_expert_compute
+
+        T, d, E, k, I = 384, 256, 16, 4, 128
+        g = torch.Generator().manual_seed(11)
+        w1 = (torch.randn(E, d, 2 * I, generator=g) * 0.05).bfloat16()
+        w2 = (torch.randn(E, I, d, generator=g) * 0.05).bfloat16()
+        problems = []
+        for r in range(world):
+            x = torch.randn(T, d, generator=g).bfloat16()
+            logits = torch.randn(T, E, generator=g)
+            logits[:, 3] += 3.0                      # skew: expert 3 is popular
+            top, idx = torch.topk(logits, k, dim=-1, sorted=False)
+            problems.append((x, torch.softmax(top, -1).bfloat16(), idx, torch.randn(T, d, generator=g).bfloat16()))
+        load = torch.bincount(torch.cat([p[2].reshape(-1) for p in problems]), minlength=E)
+        remap = balanced_placement(load, world)     # logical expert -> position in the sharded weights
+        e_local = E // world
+        position = torch.argsort(remap)             # position -> logical expert
+        mine = position[rank * e_local:(rank + 1) * e_local]
+        x, scores, idx, grad = [t.to(device) for t in problems[rank]]
+        results = {}
+        context = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, device)
+        for mode in ("peer", "collective"):
+            leaves = [x.clone().requires_grad_(), scores.clone().requires_grad_(),
+                      w1[mine].to(device).requires_grad_(), w2[mine].to(device).requires_grad_()]
+            out = ep_expert_compute(leaves[0], leaves[1], remap.to(device)[idx], leaves[2], leaves[3], E, "swiglu",
+                                    context=context if mode == "peer" else None)
+            out.backward(grad)
+            torch.cuda.synchronize()
+            results[mode] = [out.detach().float().cpu()] + [t.grad.float().cpu() for t in leaves]
+        queue.put((rank, results, mine))
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_two_gpu_ranks_both_modes_against_the_oracle(native):
+    """Runs only where two GPUs are visible: expert parallel over 2 ranks (peer memory and NCCL all-to-all, with a
+    load-balanced placement) against the single-process fp32 oracle."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    queue = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gpu_ep_worker, args=(r, world, port, queue)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        rank, results, mine = queue.get(timeout=300)
+        got[rank] = (results, mine)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+
+    T, d, E, k, I = 384, 256, 16, 4, 128
+    g = torch.Generator().manual_seed(11)
+    w1 = (torch.randn(E, d, 2 * I, generator=g) * 0.05).bfloat16().float()
+    w2 = (torch.randn(E, I, d, generator=g) * 0.05).bfloat16().float()
+    dw1_sum, dw2_sum = torch.zeros_like(w1), torch.zeros_like(w2)
+    refs = []
+    for r in range(world):
+        x = torch.randn(T, d, generator=g).bfloat16().float()
+        logits = torch.randn(T, E, generator=g)
+        logits[:, 3] += 3.0
+        top, idx = torch.topk(logits, k, dim=-1, sorted=False)
+        scores = torch.softmax(top, -1).bfloat16().float()
+        grad = torch.randn(T, d, generator=g).bfloat16().float()
+        out, dx, ds, dw1, dw2 = O.layer_fwd_bwd(x, scores, idx, w1, w2, "swiglu", grad)
+        dw1_sum += dw1
+        dw2_sum += dw2
+        refs.append((out, dx, ds))
+    rel = lambda a, b: float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+    for r in range(world):
+        results, mine = got[r]
+        for mode in ("peer", "collective"):
+            out, dx, ds, dw1, dw2 = results[mode]
+            assert rel(out, refs[r][0]) <= 2e-2 and rel(dx, refs[r][1]) <= 2e-2 and rel(ds, refs[r][2]) <= 2e-2, mode
+            assert rel(dw1, dw1_sum[mine]) <= 2e-2 and rel(dw2, dw2_sum[mine]) <= 2e-2, mode
+        for a, b in zip(results["peer"], results["collective"]):
+            assert torch.equal(a, b)    # same kernels on the same rows in the same order
