@@ -80,10 +80,11 @@ int64_t moe_mtiles_bound(int64_t num_rows, int num_experts);
  *   row_src       int32 [RP]     flat position held by padded row p, or -1 for padding
  *   dst_row       int32 [R]      padded row that holds flat position j (inverse of row_src)
  *   mtile_expert  int32 [moe_mtiles_bound]  expert of each 128-row tile
- *   tile_pairs    int32 [moe_mtiles_bound]  row tiles grouped in pairs of the same expert (two
- *                                row tiles share one weight tile on a pair of SMs): entry p = first
+ *   tile_pairs    int32 [moe_mtiles_bound + E + 1]  row tiles grouped in pairs of the same expert
+ *                                (two row tiles share one weight tile on a pair of SMs): entry p = first
  *                                tile (bits 0-19) | expert (bits 20-30) | bit 31 when tile+1 is in
- *                                the pair too
+ *                                the pair too; from index moe_mtiles_bound on, the exclusive prefix of
+ *                                the per-expert pair counts ([E+1] entries)
  *   num_mtiles    int32 [2]      {number of 128-row tiles in use, number of tile pairs}
  * Any of perm / row_src / dst_row / (mtile_expert, tile_pairs, num_mtiles) may be NULL to skip it.
  * ids outside [0, E) are rejected on the device: they are dropped from every output and
@@ -137,13 +138,14 @@ int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src,
  * for padded rows p < 128*num_mtiles, zeros where src_rank[p] < 0.  peer_bases is a DEVICE array with
  * one base pointer per rank of the node (peer-mapped buffers of [*, cols] rows, e.g. symmetric memory);
  * rows are read with ordinary loads over NVLink.  scale (fp32, may be NULL) is applied in fp32.
- * chunk_count > 1 restricts the call to the rows of chunk `chunk_index` of `chunk_count` equal slices of
- * the tile-pair list (see moe_mgrouped_gemm); num_mtiles is then the int32[2] of moe_routing_metadata.
+ * chunk_count > 1 restricts the call to the rows of the experts [E*chunk_index/chunk_count,
+ * E*(chunk_index+1)/chunk_count) (see moe_mgrouped_gemm); tile_pairs and num_experts are needed then.
  * No counterpart in the reference (it is single-GPU). */
 int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank,
                          const int32_t* src_row, const float* scale, const int32_t* num_mtiles,
-                         const int32_t* tile_pairs, int chunk_index, int chunk_count, void* dst,
-                         int64_t padded_rows, int cols, int dtype, void* stream);
+                         const int32_t* tile_pairs, int num_experts, int chunk_index,
+                         int chunk_count, void* dst, int64_t padded_rows, int cols, int dtype,
+                         void* stream);
 
 /* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order. */
 int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows,
@@ -174,7 +176,9 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
 /* M-grouped: out = epilogue(a[rows of tile] @ w[expert of tile]).
  *   mtile_expert / tile_pairs / num_mtiles come from moe_routing_metadata; tile_pairs may be
  *   NULL, which selects the one-SM-per-tile kernels instead of the paired-SM ones.
- *   chunk_count > 1 processes only chunk `chunk_index` of `chunk_count` equal slices of the tile-pair list
+ *   padded_rows must be the moe_padded_rows_bound value the metadata was built with (the pair prefix is
+ *   found at tile_pairs[padded_rows / 128]).
+ *   chunk_count > 1 processes only the experts [E*chunk_index/chunk_count, E*(chunk_index+1)/chunk_count)
  *   (needs tile_pairs): a caller can run the row movement of chunk c+1 on another stream while the GEMMs
  *   of chunk c run.  chunk_count <= 1 processes everything.
  *   a    [RP, K]

@@ -73,15 +73,18 @@ chunk_histogram_kernel(const int64_t* __restrict__ ids, int64_t R, int E, int32_
 }
 
 // Pair entry layout: bits 0-19 first tile, bits 20-30 expert, bit 31 "the pair has a second tile"
-// (so one load tells a CTA pair everything about its next work item).
+// (so one load tells a CTA pair everything about its next work item).  The per-expert exclusive prefix of
+// the pair counts follows the pair list in the same buffer, at index `mtiles_bound` ([E+1] entries).
 // Tile -> expert map and the pair list for expert e, whose padded rows start at `row_begin` and span
 // `padded` rows; its pairs start at index `pair_begin`.
 __device__ __forceinline__ void write_tile_maps(int e, int32_t row_begin, int32_t padded, int32_t pair_begin,
-                                                int32_t* __restrict__ mtile_expert, int32_t* __restrict__ tile_pairs) {
+                                                int32_t* __restrict__ mtile_expert, int32_t* __restrict__ tile_pairs,
+                                                int32_t* __restrict__ pair_prefix) {
   const int first = row_begin / MOE_TILE_M;
   const int last = first + padded / MOE_TILE_M;
   for (int m = first; m < last; ++m) mtile_expert[m] = e;
   if (tile_pairs != nullptr) {
+    pair_prefix[e] = pair_begin;  // exclusive prefix of pair counts: expert e's pairs are [prefix[e], prefix[e+1])
     for (int m = first, p = pair_begin; m < last; m += 2, ++p)
       tile_pairs[p] = static_cast<int32_t>(static_cast<uint32_t>(m) | (static_cast<uint32_t>(e) << 20) |
                                            (m + 1 < last ? 0x80000000u : 0u));
@@ -93,7 +96,7 @@ __global__ void __launch_bounds__(kMaxExperts)
 scan_offsets_kernel(const int32_t* __restrict__ chunk_hist, int32_t* __restrict__ chunk_off, int64_t nchunks, int E,
                     int32_t* __restrict__ group_indices,
                     int32_t* __restrict__ pad_offsets, int32_t* __restrict__ mtile_expert,
-                    int32_t* __restrict__ tile_pairs, int32_t* __restrict__ num_mtiles) {
+                    int32_t* __restrict__ tile_pairs, int32_t* __restrict__ num_mtiles, int mtiles_bound) {
   __shared__ int32_t sh_a[kMaxExperts];
   __shared__ int32_t sh_b[kMaxExperts];
   __shared__ int32_t sh_c[kMaxExperts];
@@ -133,10 +136,12 @@ scan_offsets_kernel(const int32_t* __restrict__ chunk_hist, int32_t* __restrict_
     group_indices[e + 1] = sh_a[e];
     pad_offsets[e + 1] = sh_b[e];
     if (e == 0) { group_indices[0] = 0; pad_offsets[0] = 0; }
-    if (mtile_expert != nullptr) write_tile_maps(e, sh_b[e] - padded, padded, sh_c[e] - pairs, mtile_expert, tile_pairs);
+    int32_t* pair_prefix = tile_pairs != nullptr ? tile_pairs + mtiles_bound : nullptr;
+    if (mtile_expert != nullptr) write_tile_maps(e, sh_b[e] - padded, padded, sh_c[e] - pairs, mtile_expert, tile_pairs, pair_prefix);
     if (num_mtiles != nullptr && e == E - 1) {
       num_mtiles[0] = sh_b[e] / MOE_TILE_M;
       num_mtiles[1] = sh_c[e];
+      if (pair_prefix != nullptr) pair_prefix[E] = sh_c[e];
     }
   }
 }
@@ -180,7 +185,7 @@ place_rows_kernel(const int64_t* __restrict__ ids, int64_t R, int E, const int32
 __global__ void __launch_bounds__(kMaxExperts)
 layout_from_groups_kernel(const int32_t* __restrict__ group_indices, int64_t R, int E, int32_t* __restrict__ pad_offsets,
                           int32_t* __restrict__ mtile_expert, int32_t* __restrict__ tile_pairs,
-                          int32_t* __restrict__ num_mtiles) {
+                          int32_t* __restrict__ num_mtiles, int mtiles_bound) {
   __shared__ int32_t sh_b[kMaxExperts];
   __shared__ int32_t sh_c[kMaxExperts];
   const int e = threadIdx.x;
@@ -204,10 +209,12 @@ layout_from_groups_kernel(const int32_t* __restrict__ group_indices, int64_t R, 
   if (e < E) {
     pad_offsets[e + 1] = sh_b[e];
     if (e == 0) pad_offsets[0] = 0;
-    if (mtile_expert != nullptr) write_tile_maps(e, sh_b[e] - padded, padded, sh_c[e] - pairs, mtile_expert, tile_pairs);
+    int32_t* pair_prefix = tile_pairs != nullptr ? tile_pairs + mtiles_bound : nullptr;
+    if (mtile_expert != nullptr) write_tile_maps(e, sh_b[e] - padded, padded, sh_c[e] - pairs, mtile_expert, tile_pairs, pair_prefix);
     if (num_mtiles != nullptr && e == E - 1) {
       num_mtiles[0] = sh_b[e] / MOE_TILE_M;
       num_mtiles[1] = sh_c[e];
+      if (pair_prefix != nullptr) pair_prefix[E] = sh_c[e];
     }
   }
 }
@@ -285,7 +292,8 @@ extern "C" int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows,
     MOE_CUDA(cudaGetLastError());
   }
   scan_offsets_kernel<<<1, kMaxExperts, 0, s>>>(chunk_hist, chunk_off, chunks, num_experts, group_indices, pad_offsets,
-                                               mtile_expert, tile_pairs, num_mtiles);
+                                               mtile_expert, tile_pairs, num_mtiles,
+                                               static_cast<int>(moe_mtiles_bound(num_rows, num_experts)));
   MOE_CUDA(cudaGetLastError());
   if (chunks > 0 && (perm || row_src || dst_row)) {
     place_rows_kernel<<<blocks, kWarpsPerBlock * 32, sh, s>>>(expert_idx, num_rows, num_experts, chunk_off,
@@ -314,7 +322,8 @@ extern "C" int moe_layout_from_groups(const int32_t* group_indices, int64_t num_
     MOE_CUDA(cudaMemsetAsync(row_src, 0xFF, moe_padded_rows_bound(num_rows, num_experts) * sizeof(int32_t), s));
   }
   layout_from_groups_kernel<<<1, kMaxExperts, 0, s>>>(group_indices, num_rows, num_experts, pad_offsets, mtile_expert,
-                                                     tile_pairs, num_mtiles);
+                                                     tile_pairs, num_mtiles,
+                                                     static_cast<int>(moe_mtiles_bound(num_rows, num_experts)));
   MOE_CUDA(cudaGetLastError());
   if (num_rows > 0 && (row_src || dst_row)) {
     const int threads = 256;

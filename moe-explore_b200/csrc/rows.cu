@@ -36,15 +36,18 @@ __global__ void __launch_bounds__(kRowThreads)
 gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* __restrict__ src_rank,
                         const int32_t* __restrict__ src_row, const float* __restrict__ scale,
                         const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
-                        int chunk_index, int chunk_count, uint4* __restrict__ dst, int vec_per_row) {
-  // Row window: everything, or chunk `chunk_index` of `chunk_count` equal slices of the tile-pair list (the same
-  // slicing the grouped GEMMs use, so a caller can pipeline the pull of chunk c+1 against the GEMMs of chunk c).
+                        int num_experts, int mtiles_bound, int chunk_index, int chunk_count, uint4* __restrict__ dst,
+                        int vec_per_row) {
+  // Row window: everything, or the rows of the experts of chunk `chunk_index` of `chunk_count` (the same slicing
+  // the grouped GEMMs use, so a caller can pipeline the pull of chunk c+1 against the GEMMs of chunk c).
   int64_t row_begin = 0;
   int64_t row_end = static_cast<int64_t>(num_mtiles[0]) * MOE_TILE_M;
   if (chunk_count > 1) {
+    const int32_t* pair_prefix = tile_pairs + mtiles_bound;
     const int pairs = num_mtiles[1];
-    const int p0 = static_cast<int>(static_cast<long long>(pairs) * chunk_index / chunk_count);
-    const int p1 = static_cast<int>(static_cast<long long>(pairs) * (chunk_index + 1) / chunk_count);
+    const int e0 = static_cast<int>(static_cast<long long>(num_experts) * chunk_index / chunk_count);
+    const int e1 = static_cast<int>(static_cast<long long>(num_experts) * (chunk_index + 1) / chunk_count);
+    const int p0 = pair_prefix[e0], p1 = pair_prefix[e1];
     if (p1 < pairs) row_end = static_cast<int64_t>(tile_pairs[p1] & 0xFFFFF) * MOE_TILE_M;
     row_begin = p0 < pairs ? static_cast<int64_t>(tile_pairs[p0] & 0xFFFFF) * MOE_TILE_M : row_end;
   }
@@ -204,25 +207,28 @@ extern "C" int moe_gather_rows(const void* src, int64_t src_rows, const int32_t*
 
 extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank, const int32_t* src_row,
                                     const float* scale, const int32_t* num_mtiles, const int32_t* tile_pairs,
-                                    int chunk_index, int chunk_count, void* dst, int64_t padded_rows, int cols,
-                                    int dtype, void* stream) {
+                                    int num_experts, int chunk_index, int chunk_count, void* dst,
+                                    int64_t padded_rows, int cols, int dtype, void* stream) {
   MOE_CHECK_ARG(peer_bases && src_rank && src_row && num_mtiles && dst, "moe_gather_rows_peer: null pointer argument");
   MOE_CHECK_ARG(aligned16(dst), "moe_gather_rows_peer: dst must be 16-byte aligned");
   MOE_CHECK_ARG(padded_rows > 0, "moe_gather_rows_peer: bad sizes");
-  MOE_CHECK_ARG(chunk_count <= 1 || (tile_pairs != nullptr && chunk_index >= 0 && chunk_index < chunk_count),
-                "moe_gather_rows_peer: chunk %d of %d needs tile_pairs and 0 <= index < count", chunk_index, chunk_count);
+  MOE_CHECK_ARG(chunk_count <= 1 || (tile_pairs != nullptr && num_experts > 0 && chunk_index >= 0 && chunk_index < chunk_count),
+                "moe_gather_rows_peer: chunk %d of %d needs tile_pairs, num_experts and 0 <= index < count", chunk_index,
+                chunk_count);
+  const int mtiles_bound = static_cast<int>(padded_rows / MOE_TILE_M);
   MOE_ROW_COMMON_CHECKS("moe_gather_rows_peer", cols, dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = row_grid(padded_rows);
   const uint4* const* bases = reinterpret_cast<const uint4* const*>(peer_bases);
   if (dtype == MOE_DTYPE_BF16) {
     gather_rows_peer_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
-                                                                       tile_pairs, chunk_index, chunk_count,
+                                                                       tile_pairs, num_experts, mtiles_bound,
+                                                                       chunk_index, chunk_count,
                                                                        static_cast<uint4*>(dst), cols / 8);
   } else {
     gather_rows_peer_kernel<__half><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
-                                                                chunk_index, chunk_count, static_cast<uint4*>(dst),
-                                                                cols / 8);
+                                                                num_experts, mtiles_bound, chunk_index, chunk_count,
+                                                                static_cast<uint4*>(dst), cols / 8);
   }
   MOE_CUDA(cudaGetLastError());
   return MOE_OK;

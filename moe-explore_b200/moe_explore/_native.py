@@ -34,7 +34,7 @@ SIGNATURES = {
     "moe_routing_metadata_static": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 9 + [c_void_p]),
     "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 6 + [c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
-    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
+    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_mgrouped_gemm_push": (c_int, [c_void_p] * 8 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_combine_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
@@ -202,12 +202,14 @@ def gather_rows(src, row_src, num_mtiles, dst, div):
     _count(1)
 
 
-def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst, tile_pairs=None, chunk=(0, 1)):
+def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst, tile_pairs=None, num_experts=0,
+                     chunk=(0, 1)):
     """dst[p] = scale[p] * peer_bases[src_rank[p]][src_row[p]]; peer_bases: int64 device tensor of base pointers."""
     require_cuda(peer_bases, dst)
     with _Timed("rows:gather_peer"):
         rc = load().moe_gather_rows_peer(_ptr(peer_bases), _ptr(src_rank), _ptr(src_row), _ptr(scale), _ptr(num_mtiles),
-                                         _ptr(tile_pairs), chunk[0], chunk[1], _ptr(dst), dst.size(0), dst.size(1),
+                                         _ptr(tile_pairs), num_experts, chunk[0], chunk[1], _ptr(dst), dst.size(0),
+                                         dst.size(1),
                                          dtype_code(dst.dtype), _stream())
     _check("moe_gather_rows_peer", rc)
     _count(1)

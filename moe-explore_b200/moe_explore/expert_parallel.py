@@ -353,16 +353,21 @@ class NativePeerOps(NativeOps):
         _native.combine_bwd(grad_out, scores, y_back, perm32_padded, tiles, None, dscores, topk)
         return dscores
 
+    @staticmethod
+    def _chunks(ctx: EPContext, lay: PeerLayout) -> int:
+        """Chunks are slices of the local expert list."""
+        return max(1, min(ctx.chunks, lay.plan.num_experts))
+
     def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
         """Enqueue the pull of every chunk on the side stream; returns one event per chunk."""
-        plan, chunks = lay.plan, max(1, ctx.chunks)
+        plan, chunks = lay.plan, self._chunks(ctx, lay)
         main = torch.cuda.current_stream()
         ctx.comm_stream.wait_stream(main)          # the layout arrays and the destination exist
         events = []
         with torch.cuda.stream(ctx.comm_stream):
             for c in range(chunks):
                 _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, scale, plan.num_mtiles, dst,
-                                         plan.tile_pairs, (c, chunks))
+                                         plan.tile_pairs, plan.num_experts, (c, chunks))
                 ev = torch.cuda.Event()
                 ev.record(ctx.comm_stream)
                 events.append(ev)
@@ -371,7 +376,7 @@ class NativePeerOps(NativeOps):
     def peer_forward(self, ctx: EPContext, lay: PeerLayout, weight1, weight2, act):
         """Dispatch (pull) chunk c+1 on the side stream while the gate/up and down GEMMs of chunk c run; the
         down GEMM's epilogue pushes its rows to the token owners (combine)."""
-        plan, chunks = lay.plan, max(1, ctx.chunks)
+        plan, chunks = lay.plan, self._chunks(ctx, lay)
         rp, d = plan.padded_rows, ctx.hidden
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
         xs, hidden, pre_act = new(rp, d), new(rp, weight2.size(1)), new(rp, weight1.size(2))
@@ -388,7 +393,7 @@ class NativePeerOps(NativeOps):
 
     def peer_backward(self, ctx: EPContext, lay: PeerLayout, state, weight1, weight2, act):
         xs, hidden, pre_act = state
-        plan, chunks = lay.plan, max(1, ctx.chunks)
+        plan, chunks = lay.plan, self._chunks(ctx, lay)
         rp, d = plan.padded_rows, ctx.hidden
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
         gs, d_pre = new(rp, d), new(rp, pre_act.size(1))

@@ -26,7 +26,8 @@ class RoutingPlan:
     row_src: torch.Tensor         # int32 [RP] flat position held by padded row p, -1 for padding
     dst_row: torch.Tensor         # int32 [R]  padded row of flat position j
     mtile_expert: torch.Tensor    # int32 [RP/128] expert of each 128-row tile
-    tile_pairs: torch.Tensor      # int32 [RP/128] first tile of each same-expert tile pair (bit 31: pair has two tiles)
+    tile_pairs: torch.Tensor      # int32 [RP/128 + E + 1] pair list (first tile | expert << 20 | two tiles << 31), then
+                                  # from index RP/128 the exclusive prefix of the per-expert pair counts
     num_mtiles: torch.Tensor      # int32 [2]  {tiles in use, tile pairs in use}
     status: torch.Tensor          # int32 [1]  device status word shared by the kernels of this plan
 
@@ -46,7 +47,7 @@ def _alloc(num_rows: int, num_experts: int, device, want_perm: bool):
         row_src=torch.empty(rp, **i32),
         dst_row=torch.empty(num_rows, **i32),
         mtile_expert=torch.empty(rp // _native.TILE_M, **i32),
-        tile_pairs=torch.empty(rp // _native.TILE_M, **i32),
+        tile_pairs=torch.empty(rp // _native.TILE_M + num_experts + 1, **i32),
         num_mtiles=torch.empty(2, **i32),
         status=torch.zeros(1, **i32),
     )

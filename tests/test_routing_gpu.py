@@ -39,6 +39,14 @@ def _check_against_oracle(idx, E):
         else:
             assert first + 1 == n or int(mte[first + 1]) != int(mte[first])
     assert seen == list(range(n))
+    # the per-expert exclusive prefix of pair counts follows the pair list
+    bound = plan.mtile_expert.numel()
+    prefix = plan.tile_pairs[bound: bound + E + 1].cpu().tolist()
+    per_expert = [(int(po[e + 1]) - int(po[e])) // 128 for e in range(E)]
+    expect = [0]
+    for t in per_expert:
+        expect.append(expect[-1] + (t + 1) // 2)
+    assert prefix == expect and prefix[-1] == num_pairs
     assert torch.equal(plan.pad_offsets.cpu(), po)
     assert torch.equal(plan.row_src[: n * 128].cpu(), row_src)
     assert torch.equal(plan.dst_row.cpu(), dst_row)
