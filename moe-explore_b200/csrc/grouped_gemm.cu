@@ -1010,6 +1010,12 @@ extern "C" int moe_kgrouped_gemm(const void* a, const void* b, void* dw, const i
   args.m_dim = M;
   args.n_dim = N;
   args.out = dw;
+#ifdef MOE_GEMM_STATS
+  {
+    const char* sp = getenv("MOE_GEMM_STATS_PTR");
+    args.stats = sp != nullptr ? reinterpret_cast<long long*>(strtoull(sp, nullptr, 0)) : nullptr;
+  }
+#endif
   args.act = MOE_ACT_NONE;
   args.group_m = group_m_setting();
   args.status = status;
