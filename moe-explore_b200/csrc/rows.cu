@@ -124,27 +124,30 @@ combine_topk_kernel(const uint4* __restrict__ ys, const T* __restrict__ scores, 
   }
 }
 
-// gs[p, :] = scores[j] * dout[t, :];  dscores[j] = dot(dout[t, :], ys[p, :]);  j = row_src[p], t = j / topk
+// gs[p, :] = scores[j] * dout[t, :];  dscores[j] = dot(dout[t, :], ys[p, :]);  j = row_src[p], t = j / topk.
+// One warp per padded row (8 rows per CTA): the dot product is a warp-shuffle reduction, no block barrier.
 template <typename T>
 __global__ void __launch_bounds__(kRowThreads)
 combine_bwd_kernel(const uint4* __restrict__ dout, const T* __restrict__ scores, const uint4* __restrict__ ys,
                    const int32_t* __restrict__ row_src, const int32_t* __restrict__ num_mtiles,
                    uint4* __restrict__ gs, T* __restrict__ dscores, int topk, int vec_per_row) {
-  __shared__ float partial[kRowThreads / 32];
+  constexpr int kWarps = kRowThreads / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t rows_in_use = static_cast<int64_t>(*num_mtiles) * MOE_TILE_M;
-  for (int64_t p = blockIdx.x; p < rows_in_use; p += gridDim.x) {
+  for (int64_t p = static_cast<int64_t>(blockIdx.x) * kWarps + warp; p < rows_in_use;
+       p += static_cast<int64_t>(gridDim.x) * kWarps) {
     const int32_t j = row_src[p];
-    uint4* g = gs + p * vec_per_row;
-    if (j < 0) {
-      if (gs != nullptr)
-        for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) g[v] = make_uint4(0, 0, 0, 0);
-      continue;  // uniform across the CTA
+    uint4* g = gs != nullptr ? gs + p * vec_per_row : nullptr;
+    if (j < 0) {  // padding row (uniform across the warp)
+      if (g != nullptr)
+        for (int v = lane; v < vec_per_row; v += 32) g[v] = make_uint4(0, 0, 0, 0);
+      continue;
     }
     const float scale = Elem<T>::to_float(scores[j]);
     const uint4* d = dout + static_cast<int64_t>(j / topk) * vec_per_row;
     const uint4* y = ys + p * vec_per_row;
     float dot = 0.0f;
-    for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+    for (int v = lane; v < vec_per_row; v += 32) {
       const uint4 du = d[v];
       const uint4 yu = y[v];
       const uint32_t dw[4] = {du.x, du.y, du.z, du.w};
@@ -158,19 +161,11 @@ combine_bwd_kernel(const uint4* __restrict__ dout, const T* __restrict__ scores,
         dot = fmaf(df.y, yf.y, dot);
         ow[i] = Elem<T>::pack2(scale * df.x, scale * df.y);
       }
-      if (gs != nullptr) g[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
+      if (g != nullptr) g[v] = make_uint4(ow[0], ow[1], ow[2], ow[3]);
     }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) dot += __shfl_xor_sync(0xFFFFFFFFu, dot, off);
-    __syncthreads();  // previous iteration's readers of `partial` are done
-    if ((threadIdx.x & 31) == 0) partial[threadIdx.x >> 5] = dot;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      float total = 0.0f;
-#pragma unroll
-      for (int w = 0; w < kRowThreads / 32; ++w) total += partial[w];
-      dscores[j] = Elem<T>::from_float(total);
-    }
+    if (lane == 0) dscores[j] = Elem<T>::from_float(dot);
   }
 }
 
@@ -277,7 +272,7 @@ extern "C" int moe_combine_bwd(const void* dout, const void* scores, const void*
   MOE_CHECK_ARG(num_tokens >= 0 && topk > 0 && padded_rows > 0, "moe_combine_bwd: bad sizes");
   MOE_ROW_COMMON_CHECKS("moe_combine_bwd", cols, dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = row_grid(padded_rows);
+  const int grid = row_grid((padded_rows + kRowThreads / 32 - 1) / (kRowThreads / 32));
   if (dtype == MOE_DTYPE_BF16) {
     combine_bwd_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(
         static_cast<const uint4*>(dout), static_cast<const __nv_bfloat16*>(scores), static_cast<const uint4*>(ys),
