@@ -43,6 +43,7 @@ constexpr int BK = 64;        // K extent of one shared-memory stage: 64 x 2 byt
 constexpr int UMMA_K = 16;    // K extent of one tcgen05.mma for 16-bit inputs
 constexpr int kEpilogueWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpilogueWarps;
+constexpr int kWaveLead = 8;   // stages before the end of an item at which a worker announces the next wave
 constexpr int kDefaultGroupM = 12;  // consecutive row units that share a sweep over column tiles (L2 reuse)
 constexpr uint32_t kTmemCols = 512;
 
@@ -73,6 +74,9 @@ struct GemmArgs {
   int32_t chunk_index;  // M-grouped: process only the experts [E*index/count, E*(index+1)/count) (lets a caller
   int32_t chunk_count;  // pipeline row movement against the GEMM); count <= 1 = everything
   int32_t align_experts;  // M-grouped CTA pairs: scheduling groups never span two experts
+  uint32_t* wave_counter;  // non-null: workers start every wave_period-th work item together (grid-wide arrival
+                           // counter, zeroed by the host before the launch)
+  int32_t wave_period;
   int32_t group_m;  // row units per scheduling group
   int32_t hint_weights_stream;  // 1: weight tiles get the evict-first L2 policy
   int32_t* status;
@@ -245,6 +249,32 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const Wi
   return c;
 }
 
+// Wave barrier of the persistent workers.  With a static stride every worker's i-th work item belongs to the same
+// "wave" of neighbouring tiles; workers that share operand tiles only hit in L2 while they stream through them
+// together, and they drift apart after a few tiles (measured: DRAM reads of a long-K GEMM equal the algorithmic
+// bytes for one wave, 1.4x for two, 3.9x for eight).  The leader's producer thread of every worker therefore
+// arrives on a global counter a few stages BEFORE it finishes the items of wave i-1 and waits (bounded) at the start
+// of wave i until all workers have arrived: split like this the wait is short and the operand pipeline does not
+// drain, while workers still stay within a few stages of each other.
+__device__ __forceinline__ bool wave_wait(uint32_t* counter, uint32_t target, volatile int* abort_flag, int* status) {
+  const long long t0 = clock64();
+  int spins = 0;
+  while (true) {
+    uint32_t seen;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(counter) : "memory");
+    if (seen >= target) return true;
+    if (((++spins) & 15) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        if (status) atomicCAS(status, 0, DS_TIMEOUT_PRODUCER);
+        return false;
+      }
+    }
+    __nanosleep(64);
+  }
+}
+
 // 8 consecutive output elements (16 bytes) from 8 fp32 values.
 template <typename T>
 __device__ __forceinline__ uint4 pack8(const float* v) {
@@ -329,11 +359,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       const uint64_t pol_a = hinted ? l2_policy_evict_last() : l2_policy_evict_normal();
       const uint64_t pol_b = hinted ? l2_policy_evict_first() : l2_policy_evict_normal();
       TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, win, args, BN, rank);
-      for (int t = unit; t < ntiles && ok; t += num_units) {
+      const bool wave_sync = !KG && args.wave_counter != nullptr && rank == 0;
+      int wave = 0;
+      for (int t = unit; t < ntiles && ok; t += num_units, ++wave) {
         const TileCoord c = c_next;
         // fetch the next work item's coordinates now; the loads complete while this tile streams
         if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, win, args, BN, rank);
+        if (wave_sync && wave > 0 && wave % args.wave_period == 0 &&
+            !wave_wait(args.wave_counter, static_cast<uint32_t>(num_units) * (wave / args.wave_period), abort_flag,
+                       args.status)) {
+          ok = false;
+          break;
+        }
+        // this worker's arrival for the NEXT synchronised wave goes out kWaveLead stages before this item ends
+        const bool arrive_here = wave_sync && (wave + 1) % args.wave_period == 0;
+        const int arrive_kb = c.kiters > kWaveLead ? c.kiters - kWaveLead : 0;
         for (int kb = 0; kb < c.kiters; ++kb) {
+          if (arrive_here && kb == arrive_kb) atomicAdd(args.wave_counter, 1u);
           if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, args.status, DS_TIMEOUT_PRODUCER)) {
             ok = false;
             break;
@@ -385,6 +427,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
+      }
+      if (wave_sync) {
+        // workers without an item in the remaining waves still count, so that the others do not wait for them
+        // (arrivals for waves up to `wave` were made inside the items that preceded them)
+        const int waves = (ntiles + num_units - 1) / num_units;
+        for (int w = wave + 1; w < waves; ++w)
+          if (w % args.wave_period == 0) atomicAdd(args.wave_counter, 1u);
       }
       if (!ok) {
         // Let copies that were already issued land before the CTA releases its shared memory.
@@ -798,6 +847,29 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Arrival counters of the wave barrier: a small ring in device memory; every launch that uses the barrier takes
+// the next slot and zeroes it on its stream first.
+constexpr int kWaveSlots = 256;
+static __device__ uint32_t g_wave_counters[kWaveSlots];
+
+static int next_wave_counter(cudaStream_t stream, uint32_t** out) {
+  static uint32_t* base[16] = {};
+  static unsigned next = 0;
+  int dev = 0;
+  MOE_CUDA(cudaGetDevice(&dev));
+  uint32_t* b = dev < 16 ? base[dev] : nullptr;
+  if (b == nullptr) {
+    void* p = nullptr;
+    MOE_CUDA(cudaGetSymbolAddress(&p, g_wave_counters));
+    b = static_cast<uint32_t*>(p);
+    if (dev < 16) base[dev] = b;
+  }
+  uint32_t* slot = b + (next++ % kWaveSlots);
+  MOE_CUDA(cudaMemsetAsync(slot, 0, sizeof(uint32_t), stream));
+  *out = slot;
+  return MOE_OK;
+}
+
 // Row units per scheduling group; MOE_SM100_GROUP_M in the environment overrides it (measurement aid).
 static int group_m_setting() {
   static int cached = 0;
@@ -918,6 +990,21 @@ static int mgrouped_common(const void* a, const void* w, void* out, void* aux_ou
   args.hint_weights_stream = getenv("MOE_SM100_L2_HINT") != nullptr ? 1 : 0;
   args.status = status;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  {
+    // The wave barrier cuts the DRAM reads of every M-grouped GEMM to about the algorithmic bytes (gate/up at
+    // the Mixtral shape: 6.4 -> 2.1 GB), but only long contractions get faster (K = 14336: -1.2 %, K = 28672:
+    // -2 %); at K = 4096 the synchronised bursts on shared tiles cost more than the re-reads (+6 %).  Hence
+    // on for K >= 8192; MOE_SM100_WAVE_SYNC=0/1 overrides.
+    const char* v = getenv("MOE_SM100_WAVE_SYNC");
+    const bool on = v != nullptr ? atoi(v) != 0 : K >= 8192;
+    const char* pv = getenv("MOE_SM100_WAVE_PERIOD");
+    args.wave_period = pv != nullptr && atoi(pv) > 0 ? atoi(pv) : 1;
+    args.wave_counter = nullptr;
+    if (on) {
+      const int rc = next_wave_counter(s, &args.wave_counter);
+      if (rc != MOE_OK) return rc;
+    }
+  }
   const int bn = pick_bn(N);
   const bool pairs = tile_pairs != nullptr && use_cta_pairs();
 #define MOE_MG(TYPE)                                                                                                  \
