@@ -526,35 +526,43 @@ def run_reference(args):
     torch.set_num_threads(os.cpu_count() or 1)
     torch.manual_seed(0)
     T, d, E, k, I = w["T"], w["d"], w["E"], w["k"], w["I"]
-    # Per-step sample: a token subset against full-size expert weights.  Where all experts' fp32 weights and
-    # gradients would not fit a modest host budget (12 GB of weights), a subset of the experts is used too.
+    # Per-step sample: a token subset against full-size fp32 weights of a subset of the experts.  The oracle's
+    # cost is dominated by the per-expert weight-gradient products, so the number of experts is calibrated to
+    # the time budget (and capped at 12 GB of weights); tokens are routed top-k among the sampled experts.
     e_full = E
-    per_expert_bytes = 3 * d * I * 4
-    E = max(k, min(E, int(12e9 // per_expert_bytes)))
     per_step_budget = 150.0 / (args.steps + args.warmup)
-    w1 = torch.empty(E, d, 2 * I)
-    w2 = torch.empty(E, I, d)
-    for e in range(E):
-        w1[e].normal_(0, 0.02)
-        w2[e].normal_(0, 0.02)
-    w1.requires_grad_()
-    w2.requires_grad_()
+    e_cap = max(k, min(E, int(4e9 // (3 * d * I * 4))))   # at most ~4 GB of fp32 weights (and as much again of gradients)
 
-    def sample(t_cpu):
+    def make_weights(n):
+        w1 = torch.empty(n, d, 2 * I)
+        w2 = torch.empty(n, I, d)
+        for e in range(n):
+            w1[e].normal_(0, 0.02)
+            w2[e].normal_(0, 0.02)
+        return w1.requires_grad_(), w2.requires_grad_()
+
+    def sample(t_cpu, n):
         x = torch.randn(t_cpu, d).requires_grad_()
         grad = torch.randn(t_cpu, d)
-        top, idx = torch.topk(torch.randn(t_cpu, E), k, dim=-1, sorted=False)
+        top, idx = torch.topk(torch.randn(t_cpu, n), k, dim=-1, sorted=False)
         return x, torch.softmax(top, -1).requires_grad_(), idx, grad
 
     t_cpu = min(64, T)
-    xs = sample(t_cpu)
-    t0 = time.perf_counter()
-    cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
-    probe = time.perf_counter() - t0
+    E = e_cap
+    while True:
+        w1, w2 = make_weights(E)
+        xs = sample(t_cpu, E)
+        cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])          # first touch
+        t0 = time.perf_counter()
+        cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
+        probe = time.perf_counter() - t0
+        if probe <= per_step_budget or E <= k:
+            break
+        E = max(k, E // 2)                                    # too slow for the budget: fewer experts
     while t_cpu * 2 <= min(T, 4096) and probe * 2 < per_step_budget:
         t_cpu *= 2
-        probe *= 2
-    xs = sample(t_cpu)
+        probe *= 1.3                                          # weight-gradient cost barely depends on the tokens
+    xs = sample(t_cpu, E)
     for _ in range(args.warmup):
         cpu_step(xs[0], xs[1], xs[2], w1, w2, xs[3])
     t0 = time.perf_counter()
