@@ -13,11 +13,12 @@
 // Roles inside a CTA (320 threads, one CTA per SM):
 //   warp 0      : TMA producer  -- one lane issues cp.async.bulk.tensor tile loads into a
 //                 ring of shared-memory stages (128-byte swizzle), signalled by mbarriers;
-//   warp 1      : MMA issuer    -- one lane issues tcgen05.mma (128 x BN x 16, fp32
+//   warp 1      : MMA issuer    -- one lane issues tcgen05.mma (128 x BN x 16 per CTA, fp32
 //                 accumulators in TMEM, two accumulator stages) and tcgen05.commit;
 //   warps 2..9  : epilogue      -- tcgen05.ld the accumulator (each warp its 32-lane
-//                 quadrant and half of the columns), apply the fused epilogue, store 16-byte
-//                 vectors to global.
+//                 quadrant and half of the columns), apply the fused epilogue and store: plain
+//                 outputs through a swizzled shared-memory tile as whole 128-byte row segments
+//                 (locally or into another GPU's buffer), GLU / dGLU outputs as 16-byte vectors.
 // The accumulator of tile i+1 is produced while tile i is being drained.
 //
 // CTA pairs (template parameter CTAS = 2, launched as clusters of two): the two CTAs of a pair work

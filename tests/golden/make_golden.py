@@ -1,8 +1,8 @@
 """Generate the golden fixtures in this directory by running the REFERENCE implementation.
 
-Needs a checkout of arthurfeeney/moe-explore (default: /root/reference); it is only run where
-that checkout exists, and its outputs (*.npz next to this file) are committed so that the
-tests need nothing but the fixtures.
+Needs a checkout of arthurfeeney/moe-explore, given as the first argument or in the
+MOE_EXPLORE_REFERENCE environment variable; it is only run where that checkout exists, and its
+outputs (*.npz next to this file) are committed so that the tests need nothing but the fixtures.
 
 The reference is imported unmodified.  Three shims make its torch path run on a CPU-only host:
   * TORCHDYNAMO_DISABLE=1: its ``@torch.compile`` decorators become no-ops;
@@ -11,7 +11,7 @@ The reference is imported unmodified.  Three shims make its torch path run on a 
   * ``torch.histc`` is wrapped so that the int64-input / int32-out call in
     expert_permute.py:28-29 (CUDA-only as written) is served by ``torch.bincount``.
 
-Usage:  TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py [reference_root]
+Usage:  TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py <reference_root>
 """
 import os
 import sys
@@ -22,7 +22,9 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_ROOT = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF_ROOT = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("MOE_EXPLORE_REFERENCE", "")
+if not os.path.isdir(os.path.join(REF_ROOT, "src", "moe_explore")):
+    raise SystemExit("usage: make_golden.py <path to a moe-explore checkout>")
 sys.path.insert(0, os.path.join(REF_ROOT, "src"))
 
 import moe_explore.gpu_utils as _gpu_utils  # noqa: E402  (the reference package)
