@@ -227,6 +227,8 @@ def run_ours(args):
 
         if args.ep_mode == "peer":
             ep_context = EPContext(dist.group.WORLD, w["T"], w["d"], w["k"], x.dtype, device)
+            if args.ep_chunks:
+                ep_context.chunks = args.ep_chunks
 
     def step(x_in, g_in):
         """One forward + backward on device-resident inputs; returns (out, dx)."""
@@ -597,6 +599,8 @@ def main():
                     help="N = 1: skip the extra measurement of the expert-parallel workload on one GPU")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="N > 1: which experts each rank owns: evened out by measured load (default) or blocks of E/N")
+    ap.add_argument("--ep-chunks", type=int, default=None,
+                    help="N > 1, peer mode: slices of the local expert list the dispatch pull is pipelined in")
     ap.add_argument("--ep-mode", default="peer", choices=["peer", "collective"],
                     help="N > 1: rows over peer-mapped memory inside the kernels (default) or NCCL all-to-all")
     ap.add_argument("--router", default=None, choices=["logits", "logits_bias", "zipf", "zipf15", "degenerate"],

@@ -7,6 +7,8 @@
 // and scale_and_reduce (src/moe_explore/functional/scale_and_reduce.py:3-5).
 #include "common.cuh"
 
+#include <stdlib.h>
+
 namespace moe {
 
 constexpr int kRowThreads = 256;
@@ -213,7 +215,15 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
   const int mtiles_bound = static_cast<int>(padded_rows / MOE_TILE_M);
   MOE_ROW_COMMON_CHECKS("moe_gather_rows_peer", cols, dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int grid = row_grid(padded_rows);
+  // This kernel is bound by NVLink, not by SMs, and usually runs beside a grouped GEMM: a few CTAs per SM keep the
+  // links busy without taking issue slots from the GEMM (MOE_SM100_PEER_GATHER_CTAS overrides, for measurements).
+  static int ctas_per_sm = 0;
+  if (ctas_per_sm == 0) {
+    const char* v = getenv("MOE_SM100_PEER_GATHER_CTAS");
+    ctas_per_sm = v != nullptr && atoi(v) > 0 ? atoi(v) : 4;
+  }
+  const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;
+  const int grid = static_cast<int>(padded_rows < cap ? padded_rows : cap);
   const uint4* const* bases = reinterpret_cast<const uint4* const*>(peer_bases);
   if (dtype == MOE_DTYPE_BF16) {
     gather_rows_peer_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,

@@ -238,7 +238,7 @@ class EPContext:
         self.num_tokens, self.hidden, self.topk, self.dtype, self.device = num_tokens, hidden, topk, dtype, device
         self.rows_up = _round_up(max(num_tokens * topk, 1), 128)
         self.busy = False
-        self.chunks = 4          # slices of the local rows pipelined between the pull and the GEMMs
+        self.chunks = 8          # slices of the local expert list pipelined between the pull and the GEMMs
         self.comm_stream = None  # side stream the pulls run on (created with the buffers)
         if allocate:
             self._allocate_symmetric()
