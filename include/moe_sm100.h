@@ -134,6 +134,13 @@ int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src,
                     const int32_t* num_mtiles, void* dst, int64_t padded_rows, int cols,
                     int div, int dtype, void* stream);
 
+/* The layer's dispatch, token-major: dst[dst_row[t*topk + s], :] = src[t, :] for every token t and slot s
+ * (each token row is read once and written topk times), padding rows (row_src[p] < 0, p < 128*num_mtiles)
+ * are zeroed.  Same result as moe_gather_rows with div = topk. */
+int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* row_src,
+                      const int32_t* num_mtiles, void* dst, int64_t num_tokens, int topk,
+                      int64_t padded_rows, int cols, int dtype, void* stream);
+
 /* Expert-parallel dispatch as a pull: dst[p, :] = scale[p] * peer_bases[src_rank[p]][src_row[p], :]
  * for padded rows p < 128*num_mtiles, zeros where src_rank[p] < 0.  peer_bases is a DEVICE array with
  * one base pointer per rank of the node (peer-mapped buffers of [*, cols] rows, e.g. symmetric memory);

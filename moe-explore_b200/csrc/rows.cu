@@ -30,6 +30,37 @@ gather_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ ro
   }
 }
 
+// Token-major form of the same movement for the layer's own dispatch: dst[dst_row[t*topk + s], :] = src[t, :].
+// Every token row is read from HBM once and written topk times (the row-major gather re-reads it topk
+// times, and the tokens of an expert are scattered over the whole input).  The second part of the grid
+// zeroes the padding rows.
+__global__ void __launch_bounds__(kRowThreads)
+dispatch_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ dst_row,
+                     const int32_t* __restrict__ row_src, const int32_t* __restrict__ num_mtiles,
+                     uint4* __restrict__ dst, int64_t num_tokens, int topk, int vec_per_row, int token_blocks) {
+  if (static_cast<int>(blockIdx.x) < token_blocks) {
+    for (int64_t t = blockIdx.x; t < num_tokens; t += token_blocks) {
+      const uint4* s = src + t * vec_per_row;
+      const int32_t* rows = dst_row + t * topk;
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
+        const uint4 u = s[v];
+        for (int k = 0; k < topk; ++k) dst[static_cast<int64_t>(rows[k]) * vec_per_row + v] = u;
+      }
+    }
+  } else {
+    // padding rows: one warp per row, only rows whose row_src is negative
+    const int64_t rows_in_use = static_cast<int64_t>(*num_mtiles) * MOE_TILE_M;
+    const int warps = (gridDim.x - token_blocks) * (kRowThreads / 32);
+    const int warp = (blockIdx.x - token_blocks) * (kRowThreads / 32) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    for (int64_t p = warp; p < rows_in_use; p += warps) {
+      if (row_src[p] >= 0) continue;
+      uint4* d = dst + p * vec_per_row;
+      for (int v = lane; v < vec_per_row; v += 32) d[v] = make_uint4(0, 0, 0, 0);
+    }
+  }
+}
+
 // dst[p, :] = scale[p] * bases[src_rank[p]][src_row[p], :], zeros where src_rank[p] < 0.  `bases` holds
 // one base pointer per rank of the node: the source rows live in peers' memory and are read with
 // ordinary 16-byte loads over NVLink (this GPU's own rows through the same path).
@@ -198,6 +229,22 @@ extern "C" int moe_gather_rows(const void* src, int64_t src_rows, const int32_t*
   MOE_ROW_COMMON_CHECKS("moe_gather_rows", cols, dtype);
   gather_rows_kernel<<<row_grid(padded_rows), kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), row_src, num_mtiles, static_cast<uint4*>(dst), cols / 8, div);
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}
+
+extern "C" int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* row_src,
+                                 const int32_t* num_mtiles, void* dst, int64_t num_tokens, int topk,
+                                 int64_t padded_rows, int cols, int dtype, void* stream) {
+  MOE_CHECK_ARG(num_tokens >= 0 && topk > 0 && padded_rows > 0, "moe_dispatch_rows: bad sizes");
+  MOE_CHECK_ARG(src && dst_row && row_src && num_mtiles && dst, "moe_dispatch_rows: null pointer argument");
+  MOE_CHECK_ARG(aligned16(src) && aligned16(dst), "moe_dispatch_rows: pointers must be 16-byte aligned");
+  MOE_ROW_COMMON_CHECKS("moe_dispatch_rows", cols, dtype);
+  const int token_blocks = row_grid(num_tokens);
+  const int pad_blocks = sm_count();
+  dispatch_rows_kernel<<<token_blocks + pad_blocks, kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), dst_row, row_src, num_mtiles, static_cast<uint4*>(dst), num_tokens, topk, cols / 8,
+      token_blocks);
   MOE_CUDA(cudaGetLastError());
   return MOE_OK;
 }

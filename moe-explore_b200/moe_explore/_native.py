@@ -39,6 +39,7 @@ SIGNATURES = {
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_combine_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_combine_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
+    "moe_dispatch_rows": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
     "moe_mgrouped_gemm": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_mgrouped_gemm_dglu": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_kgrouped_gemm": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -246,6 +247,16 @@ def combine_topk(ys, scores, dst_row, out, topk):
         rc = load().moe_combine_topk(_ptr(ys), _ptr(scores), _ptr(dst_row), _ptr(out), out.size(0), topk, out.size(1),
                                      dtype_code(ys.dtype), _stream())
     _check("moe_combine_topk", rc)
+    _count(1)
+
+
+def dispatch_rows(src, dst_row, row_src, num_mtiles, dst, topk):
+    """dst[dst_row[t*topk+s]] = src[t]; padding rows of dst zeroed."""
+    require_cuda(src, dst)
+    with _Timed("rows:gather"):
+        rc = load().moe_dispatch_rows(_ptr(src), _ptr(dst_row), _ptr(row_src), _ptr(num_mtiles), _ptr(dst), src.size(0),
+                                      topk, dst.size(0), src.size(1), dtype_code(src.dtype), _stream())
+    _check("moe_dispatch_rows", rc)
     _count(1)
 
 

@@ -37,7 +37,7 @@ class ExpertCompute(torch.autograd.Function):
         new = lambda *shape: torch.empty(*shape, dtype=x.dtype, device=x.device)
 
         xs = new(rp, d)
-        _native.gather_rows(x, plan.row_src, plan.num_mtiles, xs, plan.topk)
+        _native.dispatch_rows(x, plan.dst_row, plan.row_src, plan.num_mtiles, xs, plan.topk)
         hidden = new(rp, inter)
         pre_act = new(rp, n1) if is_glu(act) else None
         _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act, plan.status,
