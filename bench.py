@@ -461,7 +461,7 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the
 # ncu capture summarised under profiles/ (null where no capture has been taken for that workload).
-TRAFFIC_BYTES = {"mixtral_8x7b": 6.3918e9 + 1.4357e9}
+TRAFFIC_BYTES = {"mixtral_8x7b": 3.6508e9 + 1.4292e9}
 
 
 # ----------------------------------------------------------------------------------------------
