@@ -271,6 +271,21 @@ def run_ours(args):
     sync_all()
     _native.LAUNCHES = 0
     _native.PROFILE = {}
+    run_step = lambda: step(x, grad_out)
+    launches_scale = 1
+    if args.cuda_graph:
+        # one captured forward+backward, replayed: removes the launch gaps that dominate small token counts
+        if world != 1:
+            raise SystemExit("--cuda-graph is a single-GPU option")
+        _native.PROFILE = None
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            step(x, grad_out)
+        launches_scale = args.steps      # the captured launches run once per replay
+        run_step = graph.replay
+        for _ in range(3):
+            run_step()
+        sync_all()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
@@ -279,11 +294,11 @@ def run_ours(args):
     sync_all()
     e0.record()
     for _ in range(args.steps):
-        step(x, grad_out)
+        run_step()
     e1.record()
     sync_all()
     ms = e0.elapsed_time(e1) / args.steps
-    launches = _native.LAUNCHES
+    launches = _native.LAUNCHES * launches_scale
     profile = _native.PROFILE
     _native.PROFILE = None
     clocks = sampler.stop() if rank == 0 else None
@@ -431,6 +446,8 @@ def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, 
                 "d2h_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world},
             "gpu_launches": launches,
         }
+        if args.cuda_graph:
+            line["config"]["cuda_graph"] = "one captured forward+backward step, replayed"
         # roofline of the dominant kernel: the gate/up grouped GEMM (4*R*d*I FLOPs per launch)
         dom = profile.get("mgrouped_gemm:glu") if profile else None
         if dom:
@@ -606,6 +623,8 @@ def main():
     ap.add_argument("--router", default=None, choices=["logits", "logits_bias", "zipf", "zipf15", "degenerate"],
                     help="override the router distribution of a logit-supplied workload")
     ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="capture one forward+backward step in a CUDA graph and time replays (one GPU, device-resident)")
     ap.add_argument("--device-only", action="store_true",
                     help="skip the end-to-end and CPU-baseline legs (for short runs under a profiler)")
     args = ap.parse_args()

@@ -190,8 +190,9 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  *   of chunk c run.  chunk_count <= 1 processes everything.
  *   a    [RP, K]
  *   w    [E, K, N] when w_transposed == 0, [E, N, K] when w_transposed == 1
- *   act  MOE_ACT_NONE/SILU/GELU: out [RP, N];  MOE_ACT_SWIGLU/GEGLU: out [RP, N/2] and,
- *        when pre_act != NULL, pre_act [RP, N] receives the un-activated product. */
+ *   act  MOE_ACT_NONE/SILU/GELU: out [RP, N];  MOE_ACT_SWIGLU/GEGLU: out [RP, N/2].
+ *        When pre_act != NULL (and act != MOE_ACT_NONE), pre_act [RP, N] receives the un-activated
+ *        product, which moe_mgrouped_gemm_dglu needs in the backward pass. */
 int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act,
                       const int32_t* mtile_expert, const int32_t* tile_pairs,
                       const int32_t* num_mtiles,
@@ -212,9 +213,11 @@ int moe_mgrouped_gemm_push(const void* a, const void* w, void* const* peer_bases
                            int num_experts, int w_transposed, int dtype, int chunk_index,
                            int chunk_count, int32_t* status, void* stream);
 
-/* Backward through the GLU: d_pre[RP, 2N] = dGLU(pre_act[RP, 2N]) * (g[RP, K] @ w[E, N, K]^T),
+/* Backward through the activation: d_pre = act'(pre_act) * (g[RP, K] @ w[E, N, K]^T),
  * i.e. for the layer: g = score-scaled dOut rows, w = weight2 [E, I, d] (N = I, K = d),
- * pre_act = the saved gate/up product.  act must be MOE_ACT_SWIGLU or MOE_ACT_GEGLU.
+ * pre_act = the product saved by the forward GEMM.
+ *   MOE_ACT_SWIGLU / MOE_ACT_GEGLU: pre_act and d_pre are [RP, 2N] (gate, up interleaved);
+ *   MOE_ACT_SILU / MOE_ACT_GELU:    pre_act and d_pre are [RP, N].
  * No counterpart in the reference (it has no backward). */
 int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, void* d_pre,
                            const int32_t* mtile_expert, const int32_t* tile_pairs,

@@ -48,7 +48,10 @@ constexpr int kWaveLead = 8;   // stages before the end of an item at which a wo
 constexpr int kDefaultGroupM = 12;  // consecutive row units that share a sweep over column tiles (L2 reuse)
 constexpr uint32_t kTmemCols = 512;
 
-enum Epilogue : int { EPI_ACT = 0, EPI_GLU = 1, EPI_DGLU = 2 };
+// EPI_ACT_AUX is EPI_ACT plus either a second output (aux_out: the un-activated product, saved for backward)
+// or a second input (aux_in: the saved product; the accumulator is multiplied by the activation's derivative
+// there).  A separate instantiation, so that the plain-store kernels of the hot path carry none of it.
+enum Epilogue : int { EPI_ACT = 0, EPI_GLU = 1, EPI_DGLU = 2, EPI_ACT_AUX = 3 };
 
 struct GemmArgs {
   // scheduling
@@ -63,8 +66,8 @@ struct GemmArgs {
   int32_t k_dim;  // M-grouped: K of the contraction
   // epilogue
   void* out;           // EPI_ACT: [rows, N]; EPI_GLU: [rows, N/2]; EPI_DGLU: [rows, 2N]
-  void* aux_out;       // EPI_GLU: un-activated product [rows, N] or null
-  const void* aux_in;  // EPI_DGLU: saved un-activated product [rows, 2N]
+  void* aux_out;       // EPI_GLU, EPI_ACT_AUX: un-activated product [rows, N] or null
+  const void* aux_in;  // EPI_DGLU: saved un-activated product [rows, 2N]; EPI_ACT_AUX: the same, [rows, N], or null
   // EPI_ACT, M-grouped only: when push_bases != null, accumulator row p is stored at row push_row[p] of the
   // [*, N] matrix based at push_bases[push_rank[p]] (another GPU's buffer, peer-mapped) instead of `out`;
   // rows with push_rank[p] < 0 are not stored.
@@ -580,14 +583,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         tc_fence_after();
       }
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + acc * BN;
-      if (EPI == EPI_ACT) {
+      if (EPI == EPI_ACT || EPI == EPI_ACT_AUX) {
         // Plain store (optionally with silu/gelu, optionally into another GPU's buffer): two 32-column
         // chunks at a time go through a swizzled shared-memory tile so that every store instruction
         // of the warp writes four 128-byte row segments instead of 32 scattered 16-byte pieces.
+        // EPI_ACT_AUX with aux_out: pass 0 stores the un-activated product there, pass 1 the activated one
+        // into out.  EPI_ACT_AUX with aux_in: one pass, accumulator * act'(saved product).
         const uint32_t stage_base = tiles_addr + kStages * Plan::kStageBytes + Plan::kBarrierBytes + (warp - 2) * (32 * 128);
         const unsigned long long my_base = reinterpret_cast<unsigned long long>(row_out + out_row * N);
+        const bool two_outputs = EPI == EPI_ACT_AUX && aux_out != nullptr;
+        const unsigned long long my_aux = two_outputs ? reinterpret_cast<unsigned long long>(aux_out + out_row * N) : 0ull;
+        const int first_pass = two_outputs ? 0 : 1;
 #pragma unroll 1
         for (int chunk = chunk_begin; chunk < chunk_begin + kChunksPerWarp; chunk += 2) {
+#pragma unroll 1
+          for (int pass = first_pass; pass < 2; ++pass) {
 #pragma unroll
           for (int hc = 0; hc < 2; ++hc) {
             float v[32];
@@ -601,12 +611,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
               for (int i = 0; i < 32; ++i) v[i] = 0.0f;
             }
-            if (args.act == MOE_ACT_SILU) {
+            if (EPI == EPI_ACT_AUX && aux_in != nullptr) {
+              const int col = c.n0 + (chunk + hc) * 32;
+              const T* src = aux_in + out_row * N + col;
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
-            } else if (args.act == MOE_ACT_GELU) {
+              for (int q = 0; q < 4; ++q) {
+                const uint4 h = (row_ok && col + q * 8 < N) ? __ldg(reinterpret_cast<const uint4*>(src + q * 8))
+                                                            : make_uint4(0, 0, 0, 0);
+                const uint32_t hw[4] = {h.x, h.y, h.z, h.w};
 #pragma unroll
-              for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
+                for (int p2 = 0; p2 < 4; ++p2) {
+                  const float2 pre = Elem<T>::unpack2(hw[p2]);
+                  const bool gelu = args.act == MOE_ACT_GELU;
+                  v[q * 8 + 2 * p2] *= gelu ? dgelu_f(pre.x) : dsilu_f(pre.x);
+                  v[q * 8 + 2 * p2 + 1] *= gelu ? dgelu_f(pre.y) : dsilu_f(pre.y);
+                }
+              }
+            } else if (pass == 1) {
+              if (args.act == MOE_ACT_SILU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+              } else if (args.act == MOE_ACT_GELU) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
+              }
             }
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
@@ -618,11 +646,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
           __syncwarp();
           const int col_pair0 = c.n0 + chunk * 32;  // first of the 64 columns staged
+          const unsigned long long pass_base = pass == 0 ? my_aux : my_base;
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int r = j * 4 + (lane >> 3);   // row of the warp's 32 this lane writes in this step
             const int ck = lane & 7;             // 16-byte piece of the row's 128 bytes
-            const unsigned long long base = __shfl_sync(0xFFFFFFFFu, my_base, r);
+            const unsigned long long base = __shfl_sync(0xFFFFFFFFu, pass_base, r);
             const int ok = __shfl_sync(0xFFFFFFFFu, row_ok ? 1 : 0, r);
             uint4 u;
             const uint32_t addr = stage_base + r * 128 + ((ck ^ (r & 7)) << 4);
@@ -631,6 +660,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (ok && col < N) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(base) + col) = u;
           }
           __syncwarp();
+          }  // pass
         }
       } else {
 #pragma unroll 1
@@ -920,6 +950,9 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t padded_rows, 
   } else if (epi == EPI_GLU) {
     return w_transposed ? launch<T, BN, true, true, EPI_GLU, false, CTAS>(ta, tb, args, stream)
                         : launch<T, BN, true, false, EPI_GLU, false, CTAS>(ta, tb, args, stream);
+  } else if (epi == EPI_ACT_AUX) {
+    return w_transposed ? launch<T, BN, true, true, EPI_ACT_AUX, false, CTAS>(ta, tb, args, stream)
+                        : launch<T, BN, true, false, EPI_ACT_AUX, false, CTAS>(ta, tb, args, stream);
   }
   // EPI_DGLU is only used with the transposed weight (dAct = g @ W2^T).
   return launch<T, BN, true, true, EPI_DGLU, false, CTAS>(ta, tb, args, stream);
@@ -1046,10 +1079,11 @@ extern "C" int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* 
                                  int chunk_count, int32_t* status, void* stream) {
   MOE_CHECK_ARG(act >= MOE_ACT_NONE && act <= MOE_ACT_GEGLU, "moe_mgrouped_gemm: unknown activation %d", act);
   const bool glu = act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU;
-  return mgrouped_common(a, w, out, glu ? pre_act : nullptr, nullptr, PushTarget{}, Chunk{chunk_index, chunk_count},
+  if (!glu && (act == MOE_ACT_NONE || pre_act == nullptr)) pre_act = nullptr;  // nothing to save without an activation
+  const int epi = glu ? EPI_GLU : (pre_act != nullptr ? EPI_ACT_AUX : EPI_ACT);
+  return mgrouped_common(a, w, out, pre_act, nullptr, PushTarget{}, Chunk{chunk_index, chunk_count},
                          mtile_expert, tile_pairs, num_mtiles,
-                         padded_rows, K, N, num_experts, w_transposed, glu ? EPI_GLU : EPI_ACT, act, dtype, status,
-                         stream);
+                         padded_rows, K, N, num_experts, w_transposed, epi, act, dtype, status, stream);
 }
 
 extern "C" int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, void* d_pre,
@@ -1057,11 +1091,12 @@ extern "C" int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* 
                                       const int32_t* num_mtiles, int64_t padded_rows, int K, int N, int num_experts,
                                       int act, int dtype, int chunk_index, int chunk_count, int32_t* status,
                                       void* stream) {
-  MOE_CHECK_ARG(act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU, "moe_mgrouped_gemm_dglu: activation %d is not a GLU", act);
+  MOE_CHECK_ARG(act >= MOE_ACT_SILU && act <= MOE_ACT_GEGLU, "moe_mgrouped_gemm_dglu: activation %d has no derivative here", act);
   MOE_CHECK_ARG(pre_act != nullptr, "moe_mgrouped_gemm_dglu: pre_act is null");
+  const bool glu = act == MOE_ACT_SWIGLU || act == MOE_ACT_GEGLU;
   return mgrouped_common(g, w, d_pre, nullptr, pre_act, PushTarget{}, Chunk{chunk_index, chunk_count}, mtile_expert,
                          tile_pairs, num_mtiles, padded_rows, K, N,
-                         num_experts, 1, EPI_DGLU, act, dtype, status, stream);
+                         num_experts, 1, glu ? EPI_DGLU : EPI_ACT_AUX, act, dtype, status, stream);
 }
 
 extern "C" int moe_mgrouped_gemm_push(const void* a, const void* w, void* const* peer_bases, const int32_t* dest_rank,

@@ -3,7 +3,7 @@
 forward : gather token rows into the padded expert-sorted layout -> gate/up grouped GEMM with a
           fused GLU epilogue -> down grouped GEMM -> weighted fold of the top-k slots.
 backward: score-scaled gather of dOut (+ router-weight gradient as a row dot product) ->
-          grouped GEMM against W2^T with the GLU derivative fused -> grouped GEMM against W1^T
+          grouped GEMM against W2^T with the activation's derivative fused (GLU or plain) -> grouped GEMM against W1^T
           and an unweighted fold for dX -> two K-grouped GEMMs for the expert weight gradients.
 
 The reference's forward is topk_moe_forward (src/moe_explore/functional/topk_moe.py:16-54);
@@ -39,7 +39,9 @@ class ExpertCompute(torch.autograd.Function):
         xs = new(rp, d)
         _native.dispatch_rows(x, plan.dst_row, plan.row_src, plan.num_mtiles, xs, plan.topk)
         hidden = new(rp, inter)
-        pre_act = new(rp, n1) if is_glu(act) else None
+        # the un-activated product, needed by the backward pass (not kept for inference or without an activation)
+        keep = act is not None and any(ctx.needs_input_grad[:4])
+        pre_act = new(rp, n1) if (is_glu(act) or keep) else None
         _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act, plan.status,
                               rows=plan.num_rows)
         ys = new(rp, d)
@@ -58,8 +60,6 @@ class ExpertCompute(torch.autograd.Function):
         xs, pre_act, hidden, ys, scores, weight1, weight2 = ctx.saved_tensors
         plan: RoutingPlan = ctx.plan
         act = ctx.act
-        if not is_glu(act):
-            raise NotImplementedError("backward is implemented for the gated activations (swiglu, geglu)")
         T, d = grad_out.shape
         rp = plan.padded_rows
         grad_out = grad_out.contiguous()
@@ -68,9 +68,13 @@ class ExpertCompute(torch.autograd.Function):
         gs = new(rp, d)
         d_scores = new(T, plan.topk)
         _native.combine_bwd(grad_out, scores, ys, plan.row_src, plan.num_mtiles, gs, d_scores, plan.topk)
-        d_pre = new(rp, pre_act.size(1))
-        _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, act, plan.status,
-                                   rows=plan.num_rows)
+        d_pre = new(rp, weight1.size(2))
+        if act is None:     # linear "activation": d_pre = gs @ W2^T
+            _native.mgrouped_gemm(gs, weight2, d_pre, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, True, None,
+                                  plan.status, rows=plan.num_rows)
+        else:
+            _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, act,
+                                       plan.status, rows=plan.num_rows)
         dxs = new(rp, d)
         _native.mgrouped_gemm(d_pre, weight1, dxs, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, True, None, plan.status,
                               rows=plan.num_rows)
