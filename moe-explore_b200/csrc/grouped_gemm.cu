@@ -567,16 +567,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
       }
       // EPI_DGLU: the saved pre-activation does not depend on the accumulator -- fetch the first
-      // chunk's 128 bytes before waiting for the MMAs, then stay one chunk ahead.
+      // chunk before waiting for the MMAs, then stay one chunk ahead.  Loads and stores are coalesced:
+      // instruction j of a chunk covers rows 4j..4j+3 of the warp's 32, eight 16-byte pieces per row
+      // (whole 128-byte lines); a swizzled 4 KB shared-memory tile per warp turns that into the
+      // row-per-lane layout of the accumulator and back.  (One row per lane straight to global memory
+      // cost 32 memory transactions per instruction and made short contractions epilogue-bound.)
       uint4 h_next[8];
       const long long ld2 = 2ll * N;
+      const int co_row = lane >> 3;  // row within a group of four
+      const int co_ck = lane & 7;    // 16-byte piece of the row's 128 bytes = 4 output columns
+      const long long warp_row0 = static_cast<long long>(c.m0) + quad * 32;
+      const uint32_t dglu_stage = tiles_addr + kStages * Plan::kStageBytes + Plan::kBarrierBytes + (warp - 2) * (32 * 128);
       if (EPI == EPI_DGLU) {
         const int col0 = c.n0 + chunk_begin * 32;
-        const T* src = aux_in + out_row * ld2 + 2 * col0;
+        const bool ok = row_ok && col0 + co_ck * 4 < N;
+        const T* src = aux_in + (warp_row0 + co_row) * ld2 + 2 * col0 + co_ck * 8;
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
-          h_next[q] = (row_ok && col0 + q * 4 < N) ? __ldg(reinterpret_cast<const uint4*>(src + q * 8))
-                                                   : make_uint4(0, 0, 0, 0);
+        for (int j = 0; j < 8; ++j)
+          h_next[j] = ok ? __ldg(reinterpret_cast<const uint4*>(src + j * 4 * ld2)) : make_uint4(0, 0, 0, 0);
       }
       if (have_acc) {
         if (!mbar_wait(tfull_bar + 8 * acc, acc_phase, abort_flag, args.status, DS_TIMEOUT_EPILOGUE)) break;
@@ -669,15 +677,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         uint4 h_cur[8];
         const int col0 = c.n0 + chunk * 32;
         if (EPI == EPI_DGLU) {
+          // this chunk's rows: coalesced registers -> shared memory -> one row per lane
 #pragma unroll
-          for (int q = 0; q < 8; ++q) h_cur[q] = h_next[q];
+          for (int j = 0; j < 8; ++j) {
+            const int r = j * 4 + co_row;
+            const uint32_t addr = dglu_stage + r * 128 + ((co_ck ^ (r & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(h_next[j].x), "r"(h_next[j].y),
+                         "r"(h_next[j].z), "r"(h_next[j].w)
+                         : "memory");
+          }
+          __syncwarp();
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const uint32_t addr = dglu_stage + lane * 128 + ((q ^ (lane & 7)) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(h_cur[q].x), "=r"(h_cur[q].y), "=r"(h_cur[q].z), "=r"(h_cur[q].w)
+                         : "r"(addr));
+          }
           if (chunk + 1 < chunk_begin + kChunksPerWarp) {
             const int ncol0 = col0 + 32;
-            const T* src = aux_in + out_row * ld2 + 2 * ncol0;
+            const bool ok = row_ok && ncol0 + co_ck * 4 < N;
+            const T* src = aux_in + (warp_row0 + co_row) * ld2 + 2 * ncol0 + co_ck * 8;
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              h_next[q] = (row_ok && ncol0 + q * 4 < N) ? __ldg(reinterpret_cast<const uint4*>(src + q * 8))
-                                                        : make_uint4(0, 0, 0, 0);
+            for (int j = 0; j < 8; ++j)
+              h_next[j] = ok ? __ldg(reinterpret_cast<const uint4*>(src + j * 4 * ld2)) : make_uint4(0, 0, 0, 0);
           }
         }
         __syncwarp();  // tcgen05.ld is warp-collective: reconverge after the masked stores below
@@ -725,11 +748,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
           for (int q = 0; q < 2; ++q)
             if ((col0 >> 1) + q * 8 < half_n) *reinterpret_cast<uint4*>(dst + q * 8) = pack8<T>(g + q * 8);
-        } else {  // EPI_DGLU: v = d(activated)[row, col0..col0+32); pre-activation pairs at columns 2*col
-          T* dst = out + out_row * ld2 + 2 * col0;
+        }
+        if (EPI == EPI_DGLU) {
+          // v = d(activated)[row, col0..col0+32); pre-activation (gate, up) pairs at columns 2*col
 #pragma unroll
           for (int q = 0; q < 8; ++q) {  // 8 pre-activation elements = 4 (gate, up) pairs per 16 bytes
-            if (col0 + q * 4 >= N) continue;
             const uint32_t hw[4] = {h_cur[q].x, h_cur[q].y, h_cur[q].z, h_cur[q].w};
             float o[8];
 #pragma unroll
@@ -741,15 +764,30 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                 act_g = gelu_f(gu.x);
                 dact_g = dgelu_f(gu.x);
               } else {
-                const float s = sigmoidf_fast(gu.x);
-                act_g = gu.x * s;
-                dact_g = s * (1.0f + gu.x * (1.0f - s));
+                const float sg = sigmoidf_fast(gu.x);
+                act_g = gu.x * sg;
+                dact_g = sg * (1.0f + gu.x * (1.0f - sg));
               }
               o[2 * p] = da * gu.y * dact_g;
               o[2 * p + 1] = da * act_g;
             }
-            *reinterpret_cast<uint4*>(dst + q * 8) = pack8<T>(o);
+            const uint4 u = pack8<T>(o);
+            const uint32_t addr = dglu_stage + lane * 128 + ((q ^ (lane & 7)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                         : "memory");
           }
+          __syncwarp();
+          const bool ok = row_ok && col0 + co_ck * 4 < N;
+          T* dst = out + (warp_row0 + co_row) * ld2 + 2 * col0 + co_ck * 8;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int r = j * 4 + co_row;
+            uint4 u;
+            const uint32_t addr = dglu_stage + r * 128 + ((co_ck ^ (r & 7)) << 4);
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(addr));
+            if (ok) *reinterpret_cast<uint4*>(dst + j * 4 * ld2) = u;
+          }
+          __syncwarp();
         }
       }
       }  // EPI != EPI_ACT
@@ -958,7 +996,10 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t padded_rows, 
   return launch<T, BN, true, true, EPI_DGLU, false, CTAS>(ta, tb, args, stream);
 }
 
-static int pick_bn(int N) { return (N % 256 == 0 || N % 128 != 0) ? 256 : 128; }
+// 256-column tiles whenever there is more than one 128-column tile of work: with CTA pairs a 256 x 128 x 16 MMA
+// takes ~144 cycles against ~158 for 256 x 256 x 16 (its operand reads from shared memory are the limit), so a
+// half-empty last 256-column tile is far cheaper than narrow tiles throughout.
+static int pick_bn(int N) { return N <= 128 ? 128 : 256; }
 
 struct PushTarget {
   void* const* bases = nullptr;
