@@ -670,6 +670,92 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           __syncwarp();
           }  // pass
         }
+      } else if (EPI == EPI_GLU) {
+        // Two 32-column chunks per round.  The un-activated product (128 bytes per row) and the activated
+        // half (64 bytes per row) each go through the warp's swizzled shared-memory tile, so that every store
+        // instruction writes whole row segments (4 rows x 128 bytes, then 8 rows x 64 bytes) instead of 32
+        // scattered 16-byte pieces.  Rows are valid or not per CTA here (no per-row mask).
+        const int half_n = N >> 1;
+#pragma unroll 1
+        for (int chunk = chunk_begin; chunk < chunk_begin + kChunksPerWarp; chunk += 2) {
+          uint4 act_pk[4];  // this lane's 32 activated values of the round
+          const int col0 = c.n0 + chunk * 32;
+#pragma unroll
+          for (int hc = 0; hc < 2; ++hc) {
+            float v[32];
+            if (have_acc) {
+              uint32_t raw[32];
+              tmem_ld_32x32(taddr + (chunk + hc) * 32, raw);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+            }
+            if (aux_out != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 u = pack8<T>(v + q * 8);
+                const uint32_t addr = dglu_stage + lane * 128 + (((hc * 4 + q) ^ (lane & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(u.x), "r"(u.y), "r"(u.z), "r"(u.w)
+                             : "memory");
+              }
+            }
+            float g[16];
+            if (args.act == MOE_ACT_GEGLU) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) g[i] = gelu_f(v[2 * i]) * v[2 * i + 1];
+            } else {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) g[i] = silu_f(v[2 * i]) * v[2 * i + 1];
+            }
+            act_pk[hc * 2] = pack8<T>(g);
+            act_pk[hc * 2 + 1] = pack8<T>(g + 8);
+          }
+          if (aux_out != nullptr) {
+            __syncwarp();
+            const bool ok = row_ok && col0 + co_ck * 8 < N;
+            T* dst = aux_out + (warp_row0 + co_row) * N + col0 + co_ck * 8;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const int r = j * 4 + co_row;
+              uint4 u;
+              const uint32_t addr = dglu_stage + r * 128 + ((co_ck ^ (r & 7)) << 4);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(addr));
+              if (ok) *reinterpret_cast<uint4*>(dst + static_cast<long long>(j) * 4 * N) = u;
+            }
+            __syncwarp();
+          }
+          // activated half: 4 pieces per row; slot = (piece | odd row << 2) ^ (row >> 1 & 3) keeps both the
+          // row-per-lane writes and the 8-rows-per-instruction reads free of bank conflicts
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int slot = (i | ((lane & 1) << 2)) ^ ((lane >> 1) & 3);
+            const uint32_t addr = dglu_stage + lane * 128 + (slot << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(act_pk[i].x), "r"(act_pk[i].y),
+                         "r"(act_pk[i].z), "r"(act_pk[i].w)
+                         : "memory");
+          }
+          __syncwarp();
+          {
+            const int hr = lane >> 2;  // row within a group of eight
+            const int hk = lane & 3;   // 16-byte piece of the row's 64 bytes
+            const int hcol = (col0 >> 1) + hk * 8;
+            const bool ok = row_ok && hcol < half_n;
+            T* dst = out + (warp_row0 + hr) * half_n + hcol;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int r = j * 8 + hr;
+              const int slot = (hk | ((r & 1) << 2)) ^ ((r >> 1) & 3);
+              uint4 u;
+              const uint32_t addr = dglu_stage + r * 128 + (slot << 4);
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(u.x), "=r"(u.y), "=r"(u.z), "=r"(u.w) : "r"(addr));
+              if (ok) *reinterpret_cast<uint4*>(dst + static_cast<long long>(j) * 8 * half_n) = u;
+            }
+          }
+          __syncwarp();
+        }
       } else {
 #pragma unroll 1
       for (int chunk = chunk_begin; chunk < chunk_begin + kChunksPerWarp; ++chunk) {
@@ -713,41 +799,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         } else {
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = 0.0f;
-        }
-        if (!row_ok || col0 >= N) {
-          // nothing to store for this lane / column chunk
-        } else if (EPI == EPI_ACT) {
-          if (args.act == MOE_ACT_SILU) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
-          } else if (args.act == MOE_ACT_GELU) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = gelu_f(v[i]);
-          }
-          T* dst = row_out + out_row * N + col0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            if (col0 + q * 8 < N) *reinterpret_cast<uint4*>(dst + q * 8) = pack8<T>(v + q * 8);
-        } else if (EPI == EPI_GLU) {
-          if (aux_out != nullptr) {
-            T* dst = aux_out + out_row * N + col0;
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              if (col0 + q * 8 < N) *reinterpret_cast<uint4*>(dst + q * 8) = pack8<T>(v + q * 8);
-          }
-          float g[16];
-          if (args.act == MOE_ACT_GEGLU) {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) g[i] = gelu_f(v[2 * i]) * v[2 * i + 1];
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) g[i] = silu_f(v[2 * i]) * v[2 * i + 1];
-          }
-          const int half_n = N >> 1;
-          T* dst = out + out_row * half_n + (col0 >> 1);
-#pragma unroll
-          for (int q = 0; q < 2; ++q)
-            if ((col0 >> 1) + q * 8 < half_n) *reinterpret_cast<uint4*>(dst + q * 8) = pack8<T>(g + q * 8);
         }
         if (EPI == EPI_DGLU) {
           // v = d(activated)[row, col0..col0+32); pre-activation (gate, up) pairs at columns 2*col
