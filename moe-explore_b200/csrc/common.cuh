@@ -110,6 +110,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of a barrier phase (try_wait may suspend the thread for a while when the phase is not
+// complete; this one returns at once).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Every wait in this library is bounded: after kWaitLimitCycles the waiter raises the
 // CTA-wide abort flag, records why in the caller's status word and returns false.  All
 // other waiters see the flag and give up too, so the kernel always terminates.
@@ -267,6 +281,15 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, 
 // `bar` is an address in the shared::cluster window (own or peer CTA).
 __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// One commit that arrives on the barrier at the same shared-memory offset in both CTAs of the pair
+// (the arrival is broadcast by the commit itself; no operand load carries a cluster qualifier).
+__device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+      "h"(static_cast<uint16_t>(3))
+      : "memory");
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives lane (base+i).

@@ -453,8 +453,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       int acc = 0;
       uint32_t acc_phase = 0;
       bool ok = true;
+      bool ready = false;  // the stage about to be consumed was already seen full
 #ifdef MOE_GEMM_STATS
-      long long st_total = clock64(), st_full = 0, st_acc = 0, st_tiles = 0;
+      long long st_total = clock64(), st_full = 0, st_acc = 0, st_tiles = 0, st_slow_n = 0, st_slow = 0, st_issue = 0, st_stages = 0;
 #endif
       TileCoord c_next = decode_tile<KG, CTAS>(unit < ntiles ? unit : 0, mt, nt, win, args, BN, rank);
       for (int t = unit; t < ntiles && ok; t += num_units) {
@@ -475,14 +476,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #ifdef MOE_GEMM_STATS
           const long long t_full0 = clock64();
 #endif
-          if (!mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, DS_TIMEOUT_MMA)) {
+          // `ready` was probed one stage ahead (below), so that the barrier's round trip to shared memory
+          // overlaps the issue of the previous stage's MMAs; only a stage that was not there yet is waited for.
+          if (!ready && !mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, DS_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
 #ifdef MOE_GEMM_STATS
-          st_full += clock64() - t_full0;
+          const long long t_full1 = clock64();
+          st_full += t_full1 - t_full0;
+          ++st_stages;
+          if (t_full1 - t_full0 > 150) { ++st_slow_n; st_slow += t_full1 - t_full0; }
 #endif
           tc_fence_after();
+          {
+            const int ns = stage + 1 == kStages ? 0 : stage + 1;
+            ready = mbar_test_wait(full_bar + 8 * ns, stage + 1 == kStages ? phase ^ 1 : phase);
+          }
           const uint32_t sa = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t sb = sa + Plan::kABytes;
 #pragma unroll
@@ -496,23 +506,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             if (kPair) umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
             else umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          // free the stage in every CTA whose shared memory these MMAs read
-          if (kPair) {
-            umma_commit_pair(empty_bar + 8 * stage);
-            umma_commit_pair(mapa_shared(empty_bar + 8 * stage, 1));
-          } else {
-            umma_commit(empty_bar + 8 * stage);
-          }
+          // free the stage in every CTA whose shared memory these MMAs read (one broadcast arrival)
+          if (kPair) umma_commit_pair_both(empty_bar + 8 * stage);
+          else umma_commit(empty_bar + 8 * stage);
+#ifdef MOE_GEMM_STATS
+          st_issue += clock64() - t_full1;
+#endif
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
         if (!ok) break;
         // accumulator complete: tell the epilogue warps of every CTA holding a part of it
-        if (kPair) {
-          umma_commit_pair(tfull_bar + 8 * acc);
-          umma_commit_pair(mapa_shared(tfull_bar + 8 * acc, 1));
-        } else {
-          umma_commit(tfull_bar + 8 * acc);
-        }
+        if (kPair) umma_commit_pair_both(tfull_bar + 8 * acc);
+        else umma_commit(tfull_bar + 8 * acc);
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok || *abort_flag) {
@@ -520,11 +525,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       }
 #ifdef MOE_GEMM_STATS
       if (args.stats != nullptr) {
-        long long* o = args.stats + 4 * blockIdx.x;
+        long long* o = args.stats + 8 * blockIdx.x;
         o[0] = clock64() - st_total;
         o[1] = st_full;
         o[2] = st_acc;
         o[3] = st_tiles;
+        o[4] = st_slow_n;
+        o[5] = st_slow;
+        o[6] = st_issue;
+        o[7] = st_stages;
       }
 #endif
     }
