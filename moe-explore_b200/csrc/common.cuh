@@ -110,6 +110,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// True in exactly one lane of a fully converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Non-blocking probe of a barrier phase (try_wait may suspend the thread for a while when the phase is not
 // complete; this one returns at once).
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {

@@ -446,7 +446,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) --------------
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the tile / stage loop (uniform control flow and operands); one elected lane issues
+    // the tensor-core instructions.
+    if (rank == 0) {
       constexpr uint32_t idesc = make_idesc<T, BN, A_K, B_K, CTAS>();
       int stage = 0;
       uint32_t phase = 0;
@@ -465,7 +467,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #ifdef MOE_GEMM_STATS
         const long long t_acc0 = clock64();
 #endif
-        if (!mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, args.status, DS_TIMEOUT_MMA)) break;
+        if (!__all_sync(0xFFFFFFFFu, mbar_wait(tempty_bar + 8 * acc, acc_phase ^ 1, abort_flag, args.status, DS_TIMEOUT_MMA))) {
+          ok = false;
+          break;
+        }
 #ifdef MOE_GEMM_STATS
         st_acc += clock64() - t_acc0;
         ++st_tiles;
@@ -478,7 +483,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #endif
           // `ready` was probed one stage ahead (below), so that the barrier's round trip to shared memory
           // overlaps the issue of the previous stage's MMAs; only a stage that was not there yet is waited for.
-          if (!ready && !mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, DS_TIMEOUT_MMA)) {
+          if (!ready && !__all_sync(0xFFFFFFFFu, mbar_wait(full_bar + 8 * stage, phase, abort_flag, args.status, DS_TIMEOUT_MMA))) {
             ok = false;
             break;
           }
@@ -491,10 +496,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           tc_fence_after();
           {
             const int ns = stage + 1 == kStages ? 0 : stage + 1;
-            ready = mbar_test_wait(full_bar + 8 * ns, stage + 1 == kStages ? phase ^ 1 : phase);
+            ready = __all_sync(0xFFFFFFFFu, mbar_test_wait(full_bar + 8 * ns, stage + 1 == kStages ? phase ^ 1 : phase));
           }
           const uint32_t sa = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t sb = sa + Plan::kABytes;
+          if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // K-major: step 16 elements (32 bytes) along the swizzled 128-byte row.
@@ -509,6 +515,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           // free the stage in every CTA whose shared memory these MMAs read (one broadcast arrival)
           if (kPair) umma_commit_pair_both(empty_bar + 8 * stage);
           else umma_commit(empty_bar + 8 * stage);
+          }
+          __syncwarp();
 #ifdef MOE_GEMM_STATS
           st_issue += clock64() - t_full1;
 #endif
@@ -516,15 +524,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         }
         if (!ok) break;
         // accumulator complete: tell the epilogue warps of every CTA holding a part of it
-        if (kPair) umma_commit_pair_both(tfull_bar + 8 * acc);
-        else umma_commit(tfull_bar + 8 * acc);
+        if (elect_one()) {
+          if (kPair) umma_commit_pair_both(tfull_bar + 8 * acc);
+          else umma_commit(tfull_bar + 8 * acc);
+        }
+        __syncwarp();
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
       if (!ok || *abort_flag) {
         for (int i = 0; i < 2000; ++i) __nanosleep(1000);
       }
 #ifdef MOE_GEMM_STATS
-      if (args.stats != nullptr) {
+      if (args.stats != nullptr && lane == 0) {
         long long* o = args.stats + 8 * blockIdx.x;
         o[0] = clock64() - st_total;
         o[1] = st_full;
