@@ -350,10 +350,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop (uniform control flow); one elected lane issues the copies.
+    {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      bool freed = false;  // the stage about to be filled was already seen free (probed one stage ahead)
       const int bcol = rank * Plan::kBCols;  // this CTA's share of the tile's B columns
       // L2 eviction priority of the operand tiles.  Default: normal priority for both.  Measured on the
       // Mixtral shape, marking the row tiles evict-last and the weight tiles evict-first RAISED the DRAM
@@ -370,8 +372,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         // fetch the next work item's coordinates now; the loads complete while this tile streams
         if (t + num_units < ntiles) c_next = decode_tile<KG, CTAS>(t + num_units, mt, nt, win, args, BN, rank);
         if (wave_sync && wave > 0 && wave % args.wave_period == 0 &&
-            !wave_wait(args.wave_counter, static_cast<uint32_t>(num_units) * (wave / args.wave_period), abort_flag,
-                       args.status)) {
+            !__all_sync(0xFFFFFFFFu, wave_wait(args.wave_counter, static_cast<uint32_t>(num_units) * (wave / args.wave_period),
+                                               abort_flag, args.status))) {
           ok = false;
           break;
         }
@@ -379,14 +381,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const bool arrive_here = wave_sync && (wave + 1) % args.wave_period == 0;
         const int arrive_kb = c.kiters > kWaveLead ? c.kiters - kWaveLead : 0;
         for (int kb = 0; kb < c.kiters; ++kb) {
-          if (arrive_here && kb == arrive_kb) atomicAdd(args.wave_counter, 1u);
-          if (!mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, args.status, DS_TIMEOUT_PRODUCER)) {
+          if (arrive_here && kb == arrive_kb && lane == 0) atomicAdd(args.wave_counter, 1u);
+          if (!freed && !__all_sync(0xFFFFFFFFu, mbar_wait(empty_bar + 8 * stage, phase ^ 1, abort_flag, args.status,
+                                                           DS_TIMEOUT_PRODUCER))) {
             ok = false;
             break;
           }
+          {
+            const int ns = stage + 1 == kStages ? 0 : stage + 1;
+            freed = __all_sync(0xFFFFFFFFu, mbar_test_wait(empty_bar + 8 * ns, stage + 1 == kStages ? phase : phase ^ 1));
+          }
           const uint32_t sa = tiles_addr + stage * Plan::kStageBytes;
           const uint32_t sb = sa + Plan::kABytes;
-          if (kPair && rank != 0) {
+          if (!elect_one()) {
+            // the other lanes only keep step
+          } else if (kPair && rank != 0) {
             // the second CTA credits the LEADER's barrier: the leader issues the MMA that reads both halves
             const uint32_t fb = mapa_shared(full_bar + 8 * stage, 0);
             mbar_arrive_expect_tx_cluster(fb, Plan::kStageBytes);
@@ -429,10 +438,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
               }
             }
           }
+          __syncwarp();
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
       }
-      if (wave_sync) {
+      if (wave_sync && lane == 0) {
         // workers without an item in the remaining waves still count, so that the others do not wait for them
         // (arrivals for waves up to `wave` were made inside the items that preceded them)
         const int waves = (ntiles + num_units - 1) / num_units;
