@@ -92,20 +92,31 @@ gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* _
       continue;
     }
     const uint4* s = bases[r] + static_cast<int64_t>(src_row[p]) * vec_per_row;
-    if (scale == nullptr) {
-      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = s[v];
-    } else {
-      const float f = scale[p];
-      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
-        const uint4 u = s[v];
-        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-        uint32_t o[4];
+    const float f = scale == nullptr ? 1.0f : scale[p];
+    // Four independent 16-byte loads per thread are issued before the first store: a remote load takes
+    // microseconds, and with load -> store -> load in program order a thread had only one in flight.
+    for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 4 * kRowThreads) {
+      uint4 u[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 x = Elem<T>::unpack2(w[i]);
-          o[i] = Elem<T>::pack2(f * x.x, f * x.y);
+      for (int i = 0; i < 4; ++i) {
+        const int v = v0 + i * kRowThreads;
+        u[i] = v < vec_per_row ? s[v] : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = v0 + i * kRowThreads;
+        if (v >= vec_per_row) continue;
+        if (scale != nullptr) {
+          const uint32_t w[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
+          uint32_t o[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 x = Elem<T>::unpack2(w[k]);
+            o[k] = Elem<T>::pack2(f * x.x, f * x.y);
+          }
+          u[i] = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        d[v] = make_uint4(o[0], o[1], o[2], o[3]);
+        d[v] = u[i];
       }
     }
   }
