@@ -226,6 +226,13 @@ int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, vo
                            int dtype, int chunk_index, int chunk_count, int32_t* status,
                            void* stream);
 
+/* Process-wide cap on the number of CTAs of every grouped-GEMM launch that follows (0 = no cap, the
+ * default: one CTA per SM).  The kernels are persistent, so a cap of sm_count - n leaves n SMs free for a
+ * kernel on another stream; the expert-parallel path uses it while rows are pulled from peer GPUs, whose
+ * loads crawl on SMs that share their L2 ingress with the GEMM's operand stream.  The value is read on the
+ * host at launch time.  No counterpart in the reference. */
+int moe_set_gemm_grid_limit(int max_ctas);
+
 /* K-grouped (expert weight gradients): dw[e] = a[rows of e]^T @ b[rows of e],
  *   a [RP, M], b [RP, N], dw [E, M, N]; experts without rows get zeros.
  * No counterpart in the reference (it has no backward). */

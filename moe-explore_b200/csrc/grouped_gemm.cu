@@ -37,6 +37,8 @@
 
 #include <stdlib.h>
 
+#include <atomic>
+
 namespace moe {
 
 constexpr int BM = 128;       // accumulator rows per CTA (= TMEM lanes)
@@ -947,6 +949,9 @@ static int make_tmap(CUtensorMap* map, int dtype, const void* ptr, int rank, con
   return MOE_OK;
 }
 
+// Process-wide cap on the CTAs of a grouped-GEMM launch (0 = none), see moe_set_gemm_grid_limit.
+static std::atomic<int> g_grid_limit{0};
+
 template <typename T, int BN, bool A_K, bool B_K, int EPI, bool KG, int CTAS>
 static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& args, cudaStream_t stream) {
   auto kernel = grouped_gemm_kernel<T, BN, A_K, B_K, EPI, KG, CTAS>;
@@ -989,6 +994,10 @@ static int launch(const CUtensorMap& ta, const CUtensorMap& tb, const GemmArgs& 
     if (getenv("MOE_SM100_DEBUG") != nullptr)
       fprintf(stderr, "[moe_sm100] grouped GEMM BN=%d CTAS=%d KG=%d: grid %d CTAs, %d bytes of shared memory\n", BN, CTAS,
               (int)KG, grid, smem);
+  }
+  {
+    const int limit = g_grid_limit.load(std::memory_order_relaxed) / CTAS * CTAS;
+    if (limit >= CTAS && limit < grid) grid = limit;
   }
   cfg.gridDim = dim3(static_cast<unsigned>(grid), 1, 1);
   MOE_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, args));
@@ -1194,6 +1203,11 @@ static int kgrouped_dispatch(const void* a, const void* b, int64_t padded_rows, 
 }  // namespace moe
 
 using namespace moe;
+
+extern "C" int moe_set_gemm_grid_limit(int max_ctas) {
+  g_grid_limit.store(max_ctas > 0 ? max_ctas : 0, std::memory_order_relaxed);
+  return MOE_OK;
+}
 
 extern "C" int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act, const int32_t* mtile_expert,
                                  const int32_t* tile_pairs, const int32_t* num_mtiles, int64_t padded_rows, int K,

@@ -42,6 +42,7 @@ SIGNATURES = {
     "moe_dispatch_rows": (c_int, [c_void_p] * 5 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
     "moe_mgrouped_gemm": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "moe_mgrouped_gemm_dglu": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "moe_set_gemm_grid_limit": (c_int, [c_int]),
     "moe_kgrouped_gemm": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
 }
 
@@ -295,6 +296,11 @@ def mgrouped_gemm_dglu(g, w, pre_act, d_pre, mtile_expert, tile_pairs, num_mtile
                                            chunk[0], chunk[1], _ptr(status), _stream())
     _check("moe_mgrouped_gemm_dglu", rc)
     _count(1)
+
+
+def set_gemm_grid_limit(max_ctas: int) -> None:
+    """Cap the CTAs of the grouped-GEMM launches that follow (0 removes the cap)."""
+    _check("moe_set_gemm_grid_limit", load().moe_set_gemm_grid_limit(int(max_ctas)))
 
 
 def kgrouped_gemm(a, b, dw, pad_offsets, status=None, rows=None, tag="dw"):
