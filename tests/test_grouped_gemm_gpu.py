@@ -191,3 +191,38 @@ def test_chunked_launches_cover_every_tile_exactly_once(chunks, native):
     plan.check()
     n = int(plan.num_mtiles[0].item()) * 128
     assert torch.equal(parts[:n], whole[:n]) and torch.equal(pre_parts[:n], pre_whole[:n])
+
+
+@pytest.mark.parametrize("limit", [2, 36, 140])
+def test_capped_grid_gives_the_same_result(limit, native):
+    """moe_set_gemm_grid_limit only changes how many persistent CTAs share the tiles (also for the long contraction
+    that uses the grid-wide wave counter, K >= 8192): outputs are bit-identical to the uncapped launch."""
+    from moe_explore.routing_plan import build_routing_plan
+
+    g = torch.Generator().manual_seed(limit)
+    E, T, K, N = 5, 3000, 8192, 512
+    idx = torch.randint(0, E, (T, 1), generator=g)
+    plan = build_routing_plan(idx.cuda(), E, 1)
+    a = torch.randn(plan.padded_rows, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(E, K, N, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    wt = (torch.randn(E, N, K, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    n = int(plan.num_mtiles[0].item()) * 128
+
+    def run():
+        out = torch.zeros(plan.padded_rows, N, dtype=torch.bfloat16, device="cuda")
+        out_t = torch.zeros_like(out)
+        native.mgrouped_gemm(a, w, out, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status)
+        native.mgrouped_gemm(a, wt, out_t, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, True, None, plan.status)
+        dw = torch.empty(E, K // 16, N, dtype=torch.bfloat16, device="cuda")
+        native.kgrouped_gemm(a[:, : K // 16].contiguous(), out, dw, plan.pad_offsets, plan.status)
+        plan.check()
+        return out[:n].clone(), out_t[:n].clone(), dw
+
+    whole = run()
+    native.set_gemm_grid_limit(limit)
+    try:
+        capped = run()
+    finally:
+        native.set_gemm_grid_limit(0)
+    for x, y in zip(whole, capped):
+        assert torch.equal(x, y)
