@@ -11,14 +11,18 @@
 //     dW1[e] = Xs_e^T @ dH_e, dW2[e] = Act_e^T @ Gs_e      A and B both MN-major
 //
 // Roles inside a CTA (320 threads, one CTA per SM):
-//   warp 0      : TMA producer  -- one lane issues cp.async.bulk.tensor tile loads into a
-//                 ring of shared-memory stages (128-byte swizzle), signalled by mbarriers;
-//   warp 1      : MMA issuer    -- one lane issues tcgen05.mma (128 x BN x 16 per CTA, fp32
-//                 accumulators in TMEM, two accumulator stages) and tcgen05.commit;
-//   warps 2..9  : epilogue      -- tcgen05.ld the accumulator (each warp its 32-lane
-//                 quadrant and half of the columns), apply the fused epilogue and store: plain
-//                 outputs through a swizzled shared-memory tile as whole 128-byte row segments
-//                 (locally or into another GPU's buffer), GLU / dGLU outputs as 16-byte vectors.
+//   warp 0      : TMA producer  -- cp.async.bulk.tensor tile loads into a ring of shared-memory
+//                 stages (128-byte swizzle), signalled by mbarriers;
+//   warp 1      : MMA issuer    -- tcgen05.mma (128 x BN x 16 per CTA, fp32 accumulators in TMEM,
+//                 two accumulator stages) and tcgen05.commit;
+//                 both warps walk their loops with all 32 lanes (uniform control flow) and let one
+//                 ELECTED lane issue; each probes the next stage's barrier one stage ahead.  (Issuing
+//                 from a single lane inside a divergent branch cost ~100 cycles per tcgen05 instruction
+//                 and left the tensor pipe idle 15 % of the time.)
+//   warps 2..9  : epilogue      -- tcgen05.ld the accumulator (each warp its 32-lane quadrant and
+//                 half of the columns), apply the fused epilogue and store through a swizzled
+//                 shared-memory tile per warp, so that every global store (and the dGLU loads) covers
+//                 whole row segments, locally or into another GPU's buffer.
 // The accumulator of tile i+1 is produced while tile i is being drained.
 //
 // CTA pairs (template parameter CTAS = 2, launched as clusters of two): the two CTAs of a pair work
@@ -28,7 +32,8 @@
 // CTAs' shared memory.  That halves the B bytes each SM pulls from L2 and reads from shared memory
 // per FLOP.  Every CTA fetches its own tiles with its own loads; nothing is broadcast.  Operand
 // arrival is credited to the leader's mbarriers, stage release and accumulator-ready signals go to
-// both CTAs (two tcgen05.commit), accumulator-drained arrivals come back to the leader.
+// both CTAs (one tcgen05.commit whose arrival is broadcast to the pair), accumulator-drained arrivals
+// come back to the leader.
 //
 // Replaces the Triton kernels m_grouped_gemm_persistent_kernel / m_grouped_gemm_inner_kernel
 // (reference: src/moe_explore/triton_kernels/m_grouped_gemm.py:33-267) and their epilogues
