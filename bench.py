@@ -229,6 +229,7 @@ def run_ours(args):
             ep_context = EPContext(dist.group.WORLD, w["T"], w["d"], w["k"], x.dtype, device)
             if args.ep_chunks:
                 ep_context.chunks = args.ep_chunks
+                ep_context.geometric = False
 
     def step(x_in, g_in):
         """One forward + backward on device-resident inputs; returns (out, dx)."""

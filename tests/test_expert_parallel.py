@@ -217,7 +217,8 @@ def test_balanced_placement_is_a_permutation_and_evens_the_load():
 
 
 @pytest.mark.gpu
-def test_single_rank_group_on_native_kernels_equals_single_gpu_path(native):
+@pytest.mark.parametrize("E", [16, 32, 80])   # 32 and more local experts: the geometric pipeline schedule
+def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, native):
     from moe_explore.expert_compute import expert_compute
     from moe_explore.expert_parallel import ep_expert_compute
     from moe_explore.routing_plan import build_routing_plan
@@ -226,7 +227,7 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(native):
     os.environ["MASTER_PORT"] = str(_free_port())
     dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
     try:
-        T, d, E, k, I = 999, 512, 16, 4, 256
+        T, d, k, I = 999, 512, 4, 256
         g = torch.Generator(device="cuda").manual_seed(2)
         mk = lambda *s, std=1.0: (torch.randn(*s, generator=g, device="cuda") * std).bfloat16()
         x, w1, w2, grad = mk(T, d), mk(E, d, 2 * I, std=0.05), mk(E, I, d, std=0.05), mk(T, d)
