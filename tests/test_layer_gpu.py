@@ -257,3 +257,28 @@ def test_forward_backward_replays_from_a_cuda_graph():
     plan.check()
     for name, a, b in zip(("out", "dx", "dlogits", "dw1", "dw2"), replayed, eager):
         assert torch.equal(a, b), f"{name}: graph replay differs from the eager path"
+
+
+@pytest.mark.gpu
+def test_expert_compute_without_activation_forward_and_backward(native):
+    """Linear experts (act=None): nothing is saved for the activation, the backward GEMM against W2^T has a plain
+    epilogue; outputs and all four gradients against the fp32 oracle."""
+    from moe_explore.expert_compute import expert_compute
+    from moe_explore.routing_plan import build_routing_plan
+
+    dev = torch.device("cuda", 0)
+    T, d, E, k, I = 700, 256, 8, 2, 384
+    g = torch.Generator(device=dev).manual_seed(5)
+    mk = lambda *s, std=1.0: (torch.randn(*s, generator=g, device=dev) * std).bfloat16()
+    x, w1, w2, grad = mk(T, d), mk(E, d, I, std=0.05), mk(E, I, d, std=0.05), mk(T, d)
+    top, idx = torch.topk(torch.randn(T, E, generator=g, device=dev), k, dim=-1, sorted=False)
+    scores = torch.softmax(top, -1).bfloat16()
+    leaves = [t.detach().clone().requires_grad_() for t in (x, scores, w1, w2)]
+    plan = build_routing_plan(idx, E, k)
+    out = expert_compute(leaves[0], leaves[1], leaves[2], leaves[3], plan, None)
+    out.backward(grad)
+    plan.check()
+    ref = O.layer_fwd_bwd(x.float(), scores.float(), idx, w1.float(), w2.float(), None, grad.float())
+    for name, a, b in zip(("out", "dx", "dscores", "dw1", "dw2"), [out] + [t.grad for t in leaves], ref):
+        assert a.isfinite().all(), name
+        assert relerr(a, b) <= TOL, f"{name}: {relerr(a, b)}"
