@@ -73,3 +73,26 @@ def test_torch_cross_check_matches_oracle_and_is_differentiable():
     torch.testing.assert_close(out, ref)
     out.sum().backward()
     assert all(t.grad is not None and torch.isfinite(t.grad).all() for t in (x, wr, w1, w2))
+
+
+@pytest.mark.parametrize("experts", [1, 5, 31, 32, 33, 64, 100, 128, 1000])
+def test_pipeline_schedule_partitions_the_local_experts(experts):
+    """Every (chunk_index, chunk_count) slice covers experts [E*i/c, E*(i+1)/c) (integer division, the formula of the
+    native entry points); the slices of a schedule must tile [0, E) in launch order, without gaps or overlaps."""
+    from types import SimpleNamespace
+
+    from moe_explore.expert_parallel import NativePeerOps
+
+    lay = SimpleNamespace(plan=SimpleNamespace(num_experts=experts))
+    for ctx in (SimpleNamespace(chunks=8, geometric=True), SimpleNamespace(chunks=8, geometric=False),
+                SimpleNamespace(chunks=3, geometric=False)):
+        schedule = NativePeerOps._chunks(ctx, lay)
+        covered = 0
+        for index, count in schedule:
+            lo, hi = experts * index // count, experts * (index + 1) // count
+            assert lo == covered and hi >= lo
+            covered = hi
+        assert covered == experts
+        if ctx.geometric and experts >= 32:
+            first = experts * 1 // 32
+            assert schedule[0] == (0, 32) and first <= experts // 8
