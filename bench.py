@@ -10,7 +10,13 @@ DeepSeek-V3-shaped expert-parallel layer, experts sharded over the ranks (launch
 Rank 0 prints ONE JSON line.
 
 ``--impl reference`` times the reference algorithm's CPU restatement (oracle/moe_oracle.py, fp32,
-all host threads) on a bounded token sample of the same workload.
+all host threads) on a bounded token sample of the same workload.  ``--impl reference_triton`` (used by the N = 1
+run for its ``gpu_baseline`` entry when a checkout of the reference is found) times the reference's own Triton
+grouped GEMMs on the GPU.
+
+Every line of our arm carries ``parity``: after the timed region the device status word is read (a non-zero code
+fails the run) and a fixed sample of tokens (every 257th) is recomputed by the fp32 oracle -- output and input
+gradient -- at every N.
 """
 from __future__ import annotations
 
@@ -23,7 +29,8 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, os.path.join(ROOT, "moe-explore_b200"))
+if "reference_triton" not in sys.argv:     # that mode imports the reference's package of the same name instead
+    sys.path.insert(0, os.path.join(ROOT, "moe-explore_b200"))
 sys.path.insert(0, ROOT)
 
 import torch  # noqa: E402
@@ -178,12 +185,77 @@ def scores_from_logits(logits, k, dtype):
     return torch.softmax(top, dim=-1, dtype=torch.float32).to(dtype), idx
 
 
+class Tracer:
+    """Observer handed to the package (``_native.TRACER``): counts this library's launches and brackets each with
+    CUDA events on the current stream, keyed by kernel variant."""
+
+    def __init__(self, timing=True):
+        self.launches = 0
+        self.timing = timing
+        self.sections = {}
+
+    def count(self, n):
+        self.launches += n
+
+    class _Section:
+        def __init__(self, owner, key, rows):
+            self.owner, self.key, self.rows = owner, key, rows
+
+        def __enter__(self):
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record()
+
+        def __exit__(self, *exc):
+            self.end.record()
+            self.owner.sections.setdefault(self.key, []).append((self.start, self.end, self.rows))
+            return False
+
+    class _Off:
+        def __enter__(self):
+            return None
+
+        def __exit__(self, *exc):
+            return False
+
+    def section(self, key, rows=None):
+        return Tracer._Section(self, key, rows) if self.timing else Tracer._Off()
+
+    def ms_per_step(self, steps):
+        return {k_: round(sum(a.elapsed_time(b) for a, b, _ in v) / steps, 4) for k_, v in sorted(self.sections.items())}
+
+
+def gate_up_key(sections):
+    for key in ("mgrouped_gemm:glu+gather", "mgrouped_gemm:glu"):
+        if key in sections:
+            return key
+    return None
+
+
+def parity_record(step_inputs, out, dx, w, idx, scores, weights, world, device, grad_out):
+    """Recompute a fixed sample of tokens (every 257th) with the fp32 oracle -- output and input gradient -- from the
+    same bf16 inputs and routing decision; returns max |a-b| / max |b| for both.  ``weights`` = (w1, w2) holding ALL
+    experts in the order ``idx`` refers to."""
+    from oracle import moe_oracle as O
+
+    T = out.size(0)
+    sample = torch.arange(0, T, 257, device=device)
+    xs = step_inputs[sample].float().requires_grad_()
+    ref = O.expert_compute(xs, scores[sample].float(), idx[sample], weights[0].detach(), weights[1].detach(), "swiglu")
+    ref.backward(grad_out[sample].float())
+    rel = lambda a, b: float((a.float() - b).abs().max() / b.abs().max().clamp_min(1e-30))
+    return {"out": rel(out[sample], ref.detach()), "dx": rel(dx[sample], xs.grad), "tokens_checked": int(sample.numel())}
+
+
 def run_ours(args):
     import torch.distributed as dist
 
     from moe_explore import _native
+    from moe_explore.expert_compute import expert_compute
     from moe_explore.functional.topk_moe import topk_moe_forward
     from moe_explore.params import MLPParams, MOEParams, TopkRouterParams
+    from moe_explore.router import router
+    from moe_explore.routing_plan import build_routing_plan, device_status
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -204,6 +276,7 @@ def run_ours(args):
         w["T"] = args.tokens
     if args.router:
         w["router"] = args.router
+    gather_in_gemm = {"auto": None, "on": True, "off": False}[args.gather_in_gemm]
     inp = make_inputs(w, device, rank, world)
     with_router = inp["router_weight"] is not None
     x, grad_out = inp["x"], inp["grad_out"]
@@ -218,18 +291,36 @@ def run_ours(args):
         from moe_explore.expert_parallel import EPContext, balanced_placement, ep_expert_compute
 
         if args.placement == "balanced":
-            # static placement from the measured expert load of this routing (all ranks' tokens)
+            # static placement from the expert load of ANOTHER batch of the same router distribution (seeded apart
+            # from the batch that is timed): what a deployment gets from load statistics of earlier steps
             with torch.no_grad():
-                _, idx0 = scores_from_logits(inp["logits"], w["k"], x.dtype)
+                pgen = torch.Generator(device=device).manual_seed(10_000 + rank)
+                other = make_logits(w, w["T"], pgen, device, rank)
+                _, idx0 = scores_from_logits(other, w["k"], x.dtype)
                 load = torch.bincount(idx0.reshape(-1), minlength=w["E"]).to(torch.int64)
+                del other
             dist.all_reduce(load)
             remap = balanced_placement(load.cpu(), world).to(device)
 
         if args.ep_mode == "peer":
             ep_context = EPContext(dist.group.WORLD, w["T"], w["d"], w["k"], x.dtype, device)
+            ep_context.pull_mode = args.ep_pull
+            if args.ep_reserved_sms is not None:
+                ep_context.reserved_sms = args.ep_reserved_sms
             if args.ep_chunks:
                 ep_context.chunks = args.ep_chunks
                 ep_context.geometric = False
+
+    def routing_of(x_in):
+        """The routing decision of one step (same ops as inside the step): scores [T,k], positions in the weights."""
+        with torch.no_grad():
+            if with_router:
+                scores, idx = router(x_in, TopkRouterParams(inp["router_weight"], w["k"], False, False))
+            else:
+                scores, idx = scores_from_logits(inp["logits"], w["k"], x_in.dtype)
+            if remap is not None:
+                idx = remap[idx]
+        return scores, idx
 
     def step(x_in, g_in):
         """One forward + backward on device-resident inputs; returns (out, dx)."""
@@ -239,15 +330,12 @@ def run_ours(args):
             if with_router:
                 params = MOEParams(TopkRouterParams(inp["router_weight"], w["k"], False, False),
                                    MLPParams(w1, w2, "swiglu"), w["E"], w["k"])
-                out = topk_moe_forward(x_in, params)
+                out = topk_moe_forward(x_in, params, gather_in_gemm=gather_in_gemm)
             else:
-                from moe_explore.expert_compute import expert_compute
-                from moe_explore.routing_plan import build_routing_plan
-
                 logits = inp["logits"].requires_grad_()
                 scores, idx = scores_from_logits(logits, w["k"], x_in.dtype)
                 plan = build_routing_plan(idx, w["E"], w["k"], want_perm=False)
-                out = expert_compute(x_in, scores, w1, w2, plan, "swiglu")
+                out = expert_compute(x_in, scores, w1, w2, plan, "swiglu", gather_in_gemm=gather_in_gemm)
         else:
             logits = inp["logits"].requires_grad_()
             scores, idx = scores_from_logits(logits, w["k"], x_in.dtype)
@@ -270,15 +358,14 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         step(x, grad_out)
     sync_all()
-    _native.LAUNCHES = 0
-    _native.PROFILE = {}
+    tracer = Tracer(timing=not args.cuda_graph)
+    _native.TRACER = tracer
     run_step = lambda: step(x, grad_out)
     launches_scale = 1
     if args.cuda_graph:
         # one captured forward+backward, replayed: removes the launch gaps that dominate small token counts
         if world != 1:
             raise SystemExit("--cuda-graph is a single-GPU option")
-        _native.PROFILE = None
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             step(x, grad_out)
@@ -299,49 +386,83 @@ def run_ours(args):
     e1.record()
     sync_all()
     ms = e0.elapsed_time(e1) / args.steps
-    launches = _native.LAUNCHES * launches_scale
-    profile = _native.PROFILE
-    _native.PROFILE = None
+    launches = tracer.launches * launches_scale
+    _native.TRACER = None
     clocks = sampler.stop() if rank == 0 else None
-    status_ok = True
 
-    e2e_ms = None
+    # ---- correctness record of the timed configuration: status word + sampled tokens against the oracle ----
+    out, dx = step(x, grad_out)
+    torch.cuda.synchronize()
+    status = torch.tensor([_native.read_status(device_status(device), reset=True)], device=device)
+    weights = (w1, w2)
+    if world > 1:
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+        # every rank needs all experts for its own sampled tokens: gather the shards (position order = idx order)
+        full = [torch.empty(w["E"], *t.shape[1:], dtype=t.dtype, device=device) for t in (w1, w2)]
+        dist.all_gather_into_tensor(full[0], w1.detach())
+        dist.all_gather_into_tensor(full[1], w2.detach())
+        weights = full
+    p_scores, p_idx = routing_of(x)
+    parity = parity_record(x, out, dx, w, p_idx, p_scores, weights, world, device, grad_out)
+    del weights
+    if world > 1:
+        full = None
+        pt = torch.tensor([parity["out"], parity["dx"]], device=device)
+        dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        parity["out"], parity["dx"] = float(pt[0]), float(pt[1])
+        parity["tokens_checked"] *= world
+    parity["status"] = int(status.item())
+    parity["tolerance"] = 2e-2
+    torch.cuda.empty_cache()
+
+    e2e = None
     if not args.device_only:
-        e2e_ms = run_e2e(args, step, x, grad_out, sync_all)
+        e2e = run_e2e(args, step, x, grad_out, sync_all)
 
     rows_per_rank = None
     if world > 1:
-        t = torch.tensor([ms, e2e_ms if e2e_ms is not None else 0.0], device=device)
+        t = torch.tensor([ms, e2e["ms"] if e2e is not None else 0.0], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), (float(t[1]) if e2e_ms is not None else None)
-        # routed rows each rank's experts received in the timed steps (same routing every step)
-        mine = [r for _, _, r in (profile or {}).get("mgrouped_gemm:glu", [])]
-        rows = torch.tensor([float(sum(mine) / max(len(mine), 1))], device=device)
+        ms = float(t[0])
+        if e2e is not None:
+            e2e["ms"] = float(t[1])
+        # routed rows each rank's experts received per step (same routing every step): sum over the chunk launches
+        mine = [r for _, _, r in tracer.sections.get("mgrouped_gemm:glu", [])]
+        rows = torch.tensor([float(sum(mine)) / args.steps], device=device)
         gathered = [torch.zeros_like(rows) for _ in range(world)]
         dist.all_gather(gathered, rows)
-        rows_per_rank = [int(g.item()) for g in gathered]
+        rows_per_rank = [int(round(g.item())) for g in gathered]
 
-    cpu_base = None
+    extras = {}
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.device_only:
-        cpu_base = cpu_baseline(w, inp, budget_s=20.0)
-    ep_base = None
-    if world == 1 and not args.device_only and not args.no_scaling_base and name == "mixtral_8x7b":
-        # the expert-parallel workload on ONE GPU (all 256 experts local): the denominator for the N > 1 lines
-        del inp, w1, w2, x, grad_out
+        extras["cpu_baseline"] = cpu_baseline(w, inp, budget_s=20.0)
+    if world == 1 and not args.device_only and name == "mixtral_8x7b" and not args.tokens:
+        del inp, w1, w2, x, grad_out, out, dx
         torch.cuda.empty_cache()
-        ep_base = measure_single_gpu(WORKLOADS["deepseek_v3_ep"], device, steps=5)
+        if not args.no_scaling_base:
+            # the expert-parallel workload on ONE GPU (all 256 experts local): the denominator for the N > 1 lines
+            extras["ep_scaling_base"] = measure_single_gpu("deepseek_v3_ep", WORKLOADS["deepseek_v3_ep"], device, steps=20,
+                                                           clocks=True, gather_in_gemm=gather_in_gemm)
+        if not args.no_other_workloads:
+            extras["other_workloads"] = other_workloads(device, gather_in_gemm)
+        if not args.no_gpu_baseline:
+            extras["gpu_baseline"] = gpu_baseline(name)
         inp = x = None
 
     if rank == 0:
-        report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank,
-               ep_base, cpu_base)
+        report(args, name, w, world, ms, e2e, launches, tracer, clocks, with_router, parity, rows_per_rank, extras)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity["status"] != 0 and parity["status"] != 4:
+        raise SystemExit(f"device status word is {parity['status']} after the timed steps: results are not valid")
+    if not (parity["out"] <= 2e-2 and parity["dx"] <= 2e-2):
+        raise SystemExit(f"sampled tokens differ from the oracle beyond 2e-2: {parity}")
 
 
 def run_e2e(args, step, x, grad_out, sync_all):
-    """End to end: pinned host buffers in, results read back, every step; returns ms per step."""
+    """End to end: pinned host buffers in, results read back, every step; returns ms per step and, from CUDA events
+    on the copy streams, the time the uploads and the read-backs took per step (they overlap the compute)."""
     hx = torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(x)
     hg = torch.empty(x.shape, dtype=x.dtype).pin_memory().copy_(grad_out)
     h_out = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for _ in range(2)]
@@ -350,24 +471,34 @@ def run_e2e(args, step, x, grad_out, sync_all):
     dev_g = [torch.empty_like(x) for _ in range(2)]
     copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
     main = torch.cuda.current_stream()
+    legs = {"h2d": [], "d2h": []}
+
+    def timed_leg(kind, stream, fn):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        fn()
+        b.record(stream)
+        legs[kind].append((a, b))
+
+    def upload(b):
+        dev_x[b].copy_(hx, non_blocking=True)
+        dev_g[b].copy_(hg, non_blocking=True)
 
     def e2e_loop(n):
         """Double-buffered: the upload of step i+1 and the read-back of step i-1 overlap step i's compute."""
         in_ready = [torch.cuda.Event(), torch.cuda.Event()]
-        out_done = [torch.cuda.Event(), torch.cuda.Event()]
         comp_done = [torch.cuda.Event(), torch.cuda.Event()]
         with torch.cuda.stream(copy_in):
-            dev_x[0].copy_(hx, non_blocking=True)
-            dev_g[0].copy_(hg, non_blocking=True)
+            timed_leg("h2d", copy_in, lambda: upload(0))
             in_ready[0].record(copy_in)
         keep = []
         for i in range(n):
             b = i & 1
             if i + 1 < n:
                 with torch.cuda.stream(copy_in):
-                    copy_in.wait_event(comp_done[b ^ 1]) if i >= 1 else None  # buffer b^1 free once step i-1 computed
-                    dev_x[b ^ 1].copy_(hx, non_blocking=True)
-                    dev_g[b ^ 1].copy_(hg, non_blocking=True)
+                    if i >= 1:
+                        copy_in.wait_event(comp_done[b ^ 1])  # buffer b^1 is free once step i-1 has computed
+                    timed_leg("h2d", copy_in, lambda: upload(b ^ 1))
                     in_ready[b ^ 1].record(copy_in)
             main.wait_event(in_ready[b])
             out, dx = step(dev_x[b], dev_g[b])
@@ -375,29 +506,41 @@ def run_e2e(args, step, x, grad_out, sync_all):
             keep.append((out, dx))
             with torch.cuda.stream(copy_out):
                 copy_out.wait_event(comp_done[b])
-                h_out[b].copy_(out, non_blocking=True)
-                h_dx[b].copy_(dx, non_blocking=True)
-                out_done[b].record(copy_out)
+
+                def download():
+                    h_out[b].copy_(out, non_blocking=True)
+                    h_dx[b].copy_(dx, non_blocking=True)
+
+                timed_leg("d2h", copy_out, download)
             if len(keep) > 2:
                 keep.pop(0)
         copy_out.synchronize()
 
     e2e_loop(3)
     sync_all()
+    legs["h2d"].clear()
+    legs["d2h"].clear()
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
     e2e_loop(args.steps)
     t1.record()
     sync_all()
-    return t0.elapsed_time(t1) / args.steps
+    leg_ms = {k_: sum(a.elapsed_time(b) for a, b in v) / max(len(v), 1) for k_, v in legs.items()}
+    nbytes = 2 * x.numel() * x.element_size()
+    return {"ms": t0.elapsed_time(t1) / args.steps, "h2d_ms": leg_ms["h2d"], "d2h_ms": leg_ms["d2h"],
+            "h2d_gbs": nbytes / leg_ms["h2d"] / 1e6 if leg_ms["h2d"] > 0 else None,
+            "d2h_gbs": nbytes / leg_ms["d2h"] / 1e6 if leg_ms["d2h"] > 0 else None}
 
 
-def measure_single_gpu(w, device, steps):
-    """Device-resident fwd+bwd time of workload ``w`` on this GPU (logit-supplied routing); tokens/s and ms."""
+def measure_single_gpu(name, w, device, steps, clocks=False, gather_in_gemm=None, cuda_graph=False):
+    """Device-resident fwd+bwd of workload ``w`` on this GPU (logit-supplied routing): timed without any
+    instrumentation, then a few more steps with per-kernel CUDA events for the dominant kernel's share."""
+    from moe_explore import _native
     from moe_explore.expert_compute import expert_compute
-    from moe_explore.routing_plan import build_routing_plan
+    from moe_explore.routing_plan import build_routing_plan, check_device_status
 
+    peaks = measured_peaks()
     inp = make_inputs(w, device)
     w1, w2 = inp["w1"].requires_grad_(), inp["w2"].requires_grad_()
     x, g, logits = inp["x"].requires_grad_(), inp["grad_out"], inp["logits"].requires_grad_()
@@ -405,76 +548,235 @@ def measure_single_gpu(w, device, steps):
     def one():
         scores, idx = scores_from_logits(logits, w["k"], x.dtype)
         plan = build_routing_plan(idx, w["E"], w["k"], want_perm=False)
-        expert_compute(x, scores, w1, w2, plan, "swiglu").backward(g)
+        expert_compute(x, scores, w1, w2, plan, "swiglu", gather_in_gemm=gather_in_gemm).backward(g)
         x.grad = w1.grad = w2.grad = logits.grad = None
 
     for _ in range(3):
         one()
     torch.cuda.synchronize()
+    run = one
+    if cuda_graph:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            one()
+        run = graph.replay
+        run()
+        torch.cuda.synchronize()
+    sampler = ClockSampler(device.index)
+    if clocks:
+        sampler.start()
+        time.sleep(0.2)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(steps):
-        one()
+        run()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
-    return {"workload": "deepseek_v3_ep", "n_gpus": 1, "value": w["T"] / (ms * 1e-3), "unit": "tokens/s",
-            "ms_per_step": ms, "tflops": algorithmic_flops(w, w["T"], False) / (ms * 1e-3) / 1e12,
-            "note": "same layer as the N > 1 runs with all experts on one GPU; divide an N-GPU value by N times this"}
+    rec = {"workload": name, "tokens": w["T"], "router": w["router"], "steps": steps, "ms_per_step": ms,
+           "value": w["T"] / (ms * 1e-3), "unit": "tokens/s",
+           "tflops": algorithmic_flops(w, w["T"], False) / (ms * 1e-3) / 1e12}
+    rec["frac_bf16_peak"] = rec["tflops"] / peaks["burst"]
+    if clocks:
+        rec["clocks"] = sampler.stop()
+    # dominant kernel (gate/up + SwiGLU) from CUDA-event brackets over a few extra steps
+    tracer = Tracer()
+    _native.TRACER = tracer
+    extra = 5
+    for _ in range(extra):
+        one()
+    torch.cuda.synchronize()
+    _native.TRACER = None
+    key = gate_up_key(tracer.sections)
+    if key:
+        durs = [a.elapsed_time(b) for a, b, _ in tracer.sections[key]]
+        avg = sum(durs) / len(durs)
+        ach = 4.0 * w["T"] * w["k"] * w["d"] * w["I"] / (avg * 1e-3) / 1e12
+        rec["dominant_kernel"] = {"name": key, "avg_launch_ms": avg, "tflops": ach, "frac": ach / peaks["sustained"]}
+    if clocks:
+        rec["section_ms_per_step"] = tracer.ms_per_step(extra)
+    rec["status"] = check_device_status(device)
+    del inp, w1, w2, x, g, logits
+    torch.cuda.empty_cache()
+    return rec
 
 
-def report(args, name, w, world, ms, e2e_ms, launches, profile, clocks, inp, x, with_router, rows_per_rank=None,
-           ep_base=None, cpu_base=None):
-    if True:
-        peaks = measured_peaks()
-        tokens = w["T"] * world
-        flops = algorithmic_flops(w, tokens, with_router)
-        line = {
-            "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "tflops": flops / (ms * 1e-3) / 1e12,
-            "frac_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["burst"],
-            "config": {"workload": name, "tokens_per_gpu": w["T"], "hidden": w["d"], "experts": w["E"], "topk": w["k"],
-                       "intermediate": w["I"], "router": w["router"], "parallelism": f"ep{world}-{args.ep_mode}" if world > 1 else "single",
-                       "expert_placement": (args.placement if world > 1 else None),
-                       "l2": "inputs larger than L2 (expert weights are re-read from HBM every step)",
-                       "flops_per_step": flops},
-            "clocks": clocks,
-            "e2e": None if e2e_ms is None else {
-                "value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world,
-                "d2h_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world},
-            "gpu_launches": launches,
-        }
-        if args.cuda_graph:
-            line["config"]["cuda_graph"] = "one captured forward+backward step, replayed"
-        # roofline of the dominant kernel: the gate/up grouped GEMM (4*R*d*I FLOPs per launch)
-        dom = profile.get("mgrouped_gemm:glu") if profile else None
-        if dom:
-            torch.cuda.synchronize()
-            durs = [a.elapsed_time(b) for a, b, _ in dom]
-            avg = sum(durs) / len(durs)
-            rows_local = sum(r for _, _, r in dom) / len(dom)  # routed rows this rank's launches handled
-            kflops = 4.0 * rows_local * w["d"] * w["I"]
-            ach = kflops / (avg * 1e-3) / 1e12
-            line["roofline"] = {"kernel": "grouped_gemm_kernel<gate/up, SwiGLU epilogue>", "bound": "tensor",
-                                "achieved": ach, "peak": peaks["sustained"], "unit": "TFLOP/s",
-                                "frac": ach / peaks["sustained"], "peak_source": peaks["source"] + " (sustained)",
-                                "frac_of_burst_peak": ach / peaks["burst"], "avg_launch_ms": avg,
-                                "launches_timed": len(durs), "rows_per_launch": rows_local, "traffic": TRAFFIC_BYTES.get(name)}
-        if rows_per_rank:
-            mean = sum(rows_per_rank) / len(rows_per_rank)
-            line["config"]["routed_rows_per_rank"] = rows_per_rank
-            line["config"]["load_imbalance_max_over_mean"] = round(max(rows_per_rank) / mean, 4) if mean else None
-        if profile:
-            line["section_ms_per_step"] = {k_: round(sum(a.elapsed_time(b) for a, b, _ in v) / args.steps, 4)
-                                           for k_, v in sorted(profile.items())}
-        if cpu_base is not None:
-            line["cpu_baseline"] = cpu_base
-        if ep_base is not None:
-            line["ep_scaling_base"] = ep_base
-        print(json.dumps(line), flush=True)
+def other_workloads(device, gather_in_gemm):
+    """The remaining single-GPU configurations, device-resident, 10 steps each: the Qwen1.5-MoE layer, the OLMoE layer
+    at 8192 tokens and the routing-stress sweep (4 token counts x 3 router distributions; the two small token counts
+    also as one captured CUDA graph, where launch gaps dominate)."""
+    out = [measure_single_gpu("qwen15_moe_a27b", WORKLOADS["qwen15_moe_a27b"], device, 10, gather_in_gemm=gather_in_gemm)]
+    for tokens in (128, 1024, 8192, 65536):
+        for router_name in ("logits", "zipf15", "degenerate"):
+            w = dict(WORKLOADS["olmoe_sweep"], T=tokens, router=router_name)
+            rec = measure_single_gpu("olmoe_sweep", w, device, 10, gather_in_gemm=gather_in_gemm)
+            if tokens <= 1024:
+                graph = measure_single_gpu("olmoe_sweep", w, device, 10, gather_in_gemm=gather_in_gemm, cuda_graph=True)
+                rec["ms_per_step_cuda_graph"] = graph["ms_per_step"]
+            out.append(rec)
+    return out
+
+
+def gpu_baseline(name):
+    """The reference's own Triton grouped GEMMs on this GPU (``--impl reference_triton`` in a child process, because
+    its package has the same name as ours), when a checkout of the reference is present; else the reason."""
+    ref = reference_checkout()
+    if ref is None:
+        return {"unavailable": "no checkout of arthurfeeney/moe-explore on this machine (MOE_EXPLORE_REFERENCE or "
+                               "baseline/_ref): the reference's Triton kernels were not timed in this run"}
+    cmd = [sys.executable, os.path.abspath(__file__), "--impl", "reference_triton", "--workload", name]
+    try:
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600,
+                           env=dict(os.environ, MOE_EXPLORE_REFERENCE=ref))
+        lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+        if r.returncode == 0 and lines:
+            return json.loads(lines[-1])
+        return {"unavailable": "the reference's Triton kernels did not run here: " + (r.stderr.strip().splitlines() or ["?"])[-1][:300]}
+    except Exception as e:   # timeout and the like
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+
+
+def reference_checkout():
+    for cand in (os.environ.get("MOE_EXPLORE_REFERENCE"), os.path.join(ROOT, "baseline", "_ref")):
+        if cand and os.path.isdir(os.path.join(cand, "src", "moe_explore")):
+            return cand
+    return None
+
+
+def generic_gemm_case(args):
+    """Seeded inputs of the stand-alone grouped-GEMM comparison: x, W1, W2, routing, and h (the down GEMM's input in
+    (token, slot) order for the scatter call)."""
+    name = args.workload or "mixtral_8x7b"
+    w = dict(WORKLOADS[name])
+    if args.tokens:
+        w["T"] = args.tokens
+    dev = torch.device("cuda", 0)
+    T, d, E, k, I = w["T"], w["d"], w["E"], w["k"], w["I"]
+    gen = torch.Generator(device=dev).manual_seed(0)
+    x = torch.randn(T, d, generator=gen, device=dev).bfloat16()
+    w1 = torch.empty(E, d, 2 * I, dtype=torch.bfloat16, device=dev)
+    w2 = torch.empty(E, I, d, dtype=torch.bfloat16, device=dev)
+    for e in range(E):
+        w1[e] = (torch.randn(d, 2 * I, generator=gen, device=dev) * 0.02).bfloat16()
+        w2[e] = (torch.randn(I, d, generator=gen, device=dev) * 0.02).bfloat16()
+    if w["router"] == "linear":
+        logits = (x @ (torch.randn(d, E, generator=gen, device=dev) * 0.02).bfloat16()).float()
+    else:
+        logits = make_logits(w, T, gen, dev)
+    scores, idx = scores_from_logits(logits, k, x.dtype)
+    h = torch.randn(T * k, I, generator=gen, device=dev).bfloat16()
+    return name, w, x, w1, w2, scores, idx, h
+
+
+def event_ms(fn, iters=10):
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def run_generic_gemms(args):
+    """The stand-alone ``m_grouped_gemm`` call with gather on W1 and with scatter on W2, without an activation, and
+    ``get_token_indices``, at a benchmark shape -- on whichever package named ``moe_explore`` is first on sys.path:
+    ``--impl reference_triton`` puts the reference's checkout there (the GPU baseline: its Triton kernels; with the
+    Triton release installed here its activation epilogue does not compile -- epilogue_split.py assigns to a tuple
+    item -- hence no activation), ``--impl ours_generic`` this repository's package."""
+    impl = args.impl
+    if impl == "reference_triton":
+        ref = reference_checkout()
+        if ref is None:
+            print(json.dumps({"impl": impl, "unavailable": "no reference checkout"}))
+            return
+        sys.path.insert(0, os.path.join(ref, "src"))
+    import moe_explore
+    from moe_explore.expert_permute import get_token_indices
+    from moe_explore.triton_kernels.m_grouped_gemm import MGroupedGEMMParams, m_grouped_gemm
+
+    if impl == "reference_triton":
+        assert os.path.abspath(ref) in os.path.abspath(moe_explore.__file__)
+    name, w, x, w1, w2, scores, idx, h = generic_gemm_case(args)
+    T, d, E, k, I = w["T"], w["d"], w["E"], w["k"], w["I"]
+    rec = {"impl": impl, "workload": name, "tokens": T}
+    with torch.no_grad():
+        p = get_token_indices(idx, k, E, zero_prefix=True)
+        gp = MGroupedGEMMParams(w1, p.group_indices, p.indices, gather=True, scatter=False, num_tokens=T, topk=k,
+                                scales=None, activation=None)
+        rec["gather_gemm_ms"] = event_ms(lambda: m_grouped_gemm(x, gp))
+        rec["gather_gemm_tflops"] = 4.0 * T * k * d * I / rec["gather_gemm_ms"] / 1e9
+        sp = MGroupedGEMMParams(w2, p.group_indices, p.indices, gather=False, scatter=True, num_tokens=T, topk=k,
+                                scales=scores, activation=None)
+        rec["scatter_gemm_ms"] = event_ms(lambda: m_grouped_gemm(h, sp))
+        rec["scatter_gemm_tflops"] = 2.0 * T * k * d * I / rec["scatter_gemm_ms"] / 1e9
+        rec["get_token_indices_ms"] = event_ms(lambda: get_token_indices(idx, k, E, zero_prefix=True))
+    print(json.dumps(rec), flush=True)
+
+
+def report(args, name, w, world, ms, e2e, launches, tracer, clocks, with_router, parity, rows_per_rank, extras):
+    peaks = measured_peaks()
+    tokens = w["T"] * world
+    flops = algorithmic_flops(w, tokens, with_router)
+    line = {
+        "metric": METRIC, "value": tokens / (ms * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "tflops": flops / (ms * 1e-3) / 1e12,
+        "frac_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["burst"],
+        "config": {"workload": name, "tokens_per_gpu": w["T"], "hidden": w["d"], "experts": w["E"], "topk": w["k"],
+                   "intermediate": w["I"], "router": w["router"],
+                   "parallelism": f"ep{world}-{args.ep_mode}" if world > 1 else "single",
+                   "expert_placement": (args.placement + " (from the expert load of another seeded batch of the same "
+                                        "router distribution)" if world > 1 and args.placement == "balanced"
+                                        else (args.placement if world > 1 else None)),
+                   "row_gather": "inside the gate/up and weight1-gradient GEMMs' operand loads (tile::gather4)"
+                                 if args.gather_in_gemm != "off" and world == 1 else "separate copy kernel / peer pull",
+                   "l2": "inputs larger than L2 (expert weights are re-read from HBM every step)",
+                   "flops_per_step": flops},
+        "clocks": clocks,
+        "e2e": None if e2e is None else {
+            "value": tokens / (e2e["ms"] * 1e-3), "unit": "tokens/s", "ms_per_step": e2e["ms"],
+            "h2d_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world,
+            "d2h_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world,
+            "rank0_h2d_ms": e2e["h2d_ms"], "rank0_d2h_ms": e2e["d2h_ms"],
+            "rank0_h2d_gbs": e2e["h2d_gbs"], "rank0_d2h_gbs": e2e["d2h_gbs"]},
+        "gpu_launches": launches,
+        "parity": parity,
+    }
+    if args.cuda_graph:
+        line["config"]["cuda_graph"] = "one captured forward+backward step, replayed"
+    if world > 1:
+        line["config"]["ep_pull"] = args.ep_pull
+    # roofline of the dominant kernel: the gate/up grouped GEMM (4*R*d*I FLOPs per launch)
+    key = gate_up_key(tracer.sections)
+    if key:
+        torch.cuda.synchronize()
+        dom = tracer.sections[key]
+        durs = [a.elapsed_time(b) for a, b, _ in dom]
+        avg = sum(durs) / len(durs)
+        rows_local = sum(r for _, _, r in dom) / len(dom)  # routed rows one launch handled
+        kflops = 4.0 * rows_local * w["d"] * w["I"]
+        ach = kflops / (avg * 1e-3) / 1e12
+        line["roofline"] = {"kernel": "grouped_gemm_kernel<gate/up, SwiGLU epilogue>" +
+                                      (" with gathered A rows" if key.endswith("+gather") else ""),
+                            "bound": "tensor",
+                            "achieved": ach, "peak": peaks["sustained"], "unit": "TFLOP/s",
+                            "frac": ach / peaks["sustained"], "peak_source": peaks["source"] + " (sustained)",
+                            "frac_of_burst_peak": ach / peaks["burst"], "avg_launch_ms": avg,
+                            "launches_timed": len(durs), "rows_per_launch": rows_local,
+                            "traffic": TRAFFIC_BYTES.get(name) if not args.tokens else None}
+    if rows_per_rank:
+        mean = sum(rows_per_rank) / len(rows_per_rank)
+        line["config"]["routed_rows_received_per_rank_per_step"] = rows_per_rank
+        line["config"]["load_imbalance_max_over_mean"] = round(max(rows_per_rank) / mean, 4) if mean else None
+    if tracer.sections:
+        line["section_ms_per_step"] = tracer.ms_per_step(args.steps)
+    line.update(extras)
+    print(json.dumps(line), flush=True)
 
 
 # DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one launch of the dominant kernel, from the
@@ -610,11 +912,25 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference_triton", "ours_generic"],
+                    help="ours / reference: the two arms of the benchmark contract; reference_triton / ours_generic: the "
+                         "stand-alone grouped-GEMM call on the reference's Triton kernels / on this library")
     ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-scaling-base", action="store_true",
                     help="N = 1: skip the extra measurement of the expert-parallel workload on one GPU")
+    ap.add_argument("--no-other-workloads", action="store_true",
+                    help="N = 1: skip the Qwen1.5-MoE / OLMoE / routing-stress-sweep measurements")
+    ap.add_argument("--no-gpu-baseline", action="store_true",
+                    help="N = 1: skip timing the reference's Triton kernels (needs a checkout of the reference)")
+    ap.add_argument("--gather-in-gemm", default="auto", choices=["auto", "on", "off"],
+                    help="single GPU: token rows gathered by the GEMMs' operand loads (auto = the package default) or "
+                         "copied into the expert-sorted layout first")
+    ap.add_argument("--ep-pull", default="bulk", choices=["bulk", "ldst"],
+                    help="N > 1, peer mode: pull rows with the copy-engine kernel on the reserved SMs or with the "
+                         "load/store kernel on all SMs")
+    ap.add_argument("--ep-reserved-sms", type=int, default=None,
+                    help="N > 1, peer mode: SMs the GEMMs leave to the pull kernels (default 8)")
     ap.add_argument("--placement", default="balanced", choices=["balanced", "contiguous"],
                     help="N > 1: which experts each rank owns: evened out by measured load (default) or blocks of E/N")
     ap.add_argument("--ep-chunks", type=int, default=None,
@@ -631,6 +947,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl in ("reference_triton", "ours_generic"):
+        run_generic_gemms(args)
     else:
         run_ours(args)
 

@@ -17,7 +17,9 @@
  *     thread-local description of the most recent failure;
  *   - `dtype` is MOE_DTYPE_BF16 or MOE_DTYPE_F16 (16-bit inputs, fp32 accumulation);
  *   - `status` (may be NULL) is a device int32 that a kernel sets to a non-zero code when
- *     one of its bounded waits runs out; the host may read it after synchronising.
+ *     one of its bounded waits runs out or its metadata is inconsistent (first code wins; the word is
+ *     never cleared by a kernel); the host reads it with moe_check_status / moe_read_status.
+ *     Callers should check it once per step: after a time-out the outputs of that launch are incomplete.
  *
  * Data layout ("padded expert-sorted rows")
  *   Routed rows (token t, slot s) have flat position j = t*topk + s.  Rows are stably
@@ -44,12 +46,14 @@ extern "C" {
 
 #define MOE_DTYPE_BF16 0
 #define MOE_DTYPE_F16 1
+#define MOE_DTYPE_F32 2 /* accepted by moe_router_topk only */
 
 #define MOE_ACT_NONE 0
 #define MOE_ACT_SILU 1
 #define MOE_ACT_GELU 2   /* exact erf form */
 #define MOE_ACT_SWIGLU 3 /* silu(even column) * odd column */
 #define MOE_ACT_GEGLU 4  /* gelu(even column) * odd column */
+#define MOE_ACT_GELU_TANH 5 /* tanh form of gelu ("approx_gelu", triton_kernels/activation.py:9-14) */
 
 #define MOE_TILE_M 128
 
@@ -61,13 +65,36 @@ const char* moe_last_error(void);
  * MOE_ERR_UNSUPPORTED when the device is not compute capability 10.x. */
 int moe_query_device(int device, int* sm_count, int* cc_major, int* cc_minor);
 
-/* Reads a device status word (synchronises `stream`); MOE_OK or MOE_ERR_TIMEOUT. */
+/* Reads a device status word (synchronises `stream`).  MOE_OK; MOE_ERR_INVALID for an expert id out of range
+ * (code 100) or metadata that does not fit the call (code 5); MOE_ERR_TIMEOUT for a wait that ran out (codes 1-3:
+ * outputs incomplete; code 4: only the wave barrier of a grouped GEMM gave up, its results are valid). */
 int moe_check_status(const int32_t* status, void* stream);
+
+/* Copies the status word into *code (host) and, when reset != 0, clears the word afterwards; synchronises `stream`. */
+int moe_read_status(const int32_t* status, int32_t* code, int reset, void* stream);
+
+/* Limit, in SM clock cycles, of every device-side wait in the launches that follow (process-wide; cycles <= 0
+ * restores the default of 2^32, about two seconds).  A wait that runs out makes its kernel set the status word,
+ * let the copies in flight land, free its tensor memory and return by itself.  No counterpart in the reference. */
+int moe_set_wait_limit_cycles(int64_t cycles);
 
 /* Upper bounds used to size buffers without reading routing results on the host:
  * padded row count RP (a multiple of MOE_TILE_M) and number of 128-row tiles. */
 int64_t moe_padded_rows_bound(int64_t num_rows, int num_experts);
 int64_t moe_mtiles_bound(int64_t num_rows, int num_experts);
+
+/* ---------------------------------------------------------------------------------
+ * Router tail in one launch: logits [T, E] -> (fp32 softmax over E when softmax_before_topk) -> top-k ->
+ * (softmax over the k selected logits otherwise) -> (division by the sum of the k when normalize) -> scores [T, k]
+ * in the logits' dtype, indices int64 [T, k], and the per-expert histogram expert_counts int32 [E] (may be NULL).
+ * Replaces the softmax / torch.topk / softmax / cast launches of topk_router (src/moe_explore/router.py:17-35); the
+ * logits GEMM stays with the caller.  Declared tie rule (torch.topk's is unspecified): equal values are taken in
+ * ascending expert index, the k results come in descending value order, NaN is never selected.  One warp per
+ * token; E <= 1024, k <= 32.  dtype: MOE_DTYPE_BF16 / F16 / F32.
+ * --------------------------------------------------------------------------------- */
+int moe_router_topk(const void* logits, void* scores, int64_t* indices, int32_t* expert_counts,
+                    int64_t num_tokens, int num_experts, int topk, int softmax_before_topk,
+                    int normalize, int dtype, void* stream);
 
 /* ---------------------------------------------------------------------------------
  * (a) Routing metadata.  Replaces get_token_indices (src/moe_explore/expert_permute.py:19-41):
@@ -85,10 +112,11 @@ int64_t moe_mtiles_bound(int64_t num_rows, int num_experts);
  *                                tile (bits 0-19) | expert (bits 20-30) | bit 31 when tile+1 is in
  *                                the pair too; from index moe_mtiles_bound on, the exclusive prefix of
  *                                the per-expert pair counts ([E+1] entries)
- *   num_mtiles    int32 [2]      {number of 128-row tiles in use, number of tile pairs}
+ *   num_mtiles    int32 [4]      {128-row tiles in use, tile pairs in use, moe_mtiles_bound(R, E), 0}
  * Any of perm / row_src / dst_row / (mtile_expert, tile_pairs, num_mtiles) may be NULL to skip it.
- * ids outside [0, E) are rejected on the device: they are dropped from every output and
- * `status` is set.  Workspace: moe_routing_workspace_bytes(R, E) bytes.
+ * ids outside [0, E) are rejected on the device: such rows are in no expert's segment, their
+ * dst_row entry and the unused tail of perm are -1 (every consumer here skips negative rows) and
+ * `status` is set to 100.  Workspace: moe_routing_workspace_bytes(R, E) bytes.
  * --------------------------------------------------------------------------------- */
 size_t moe_routing_workspace_bytes(int64_t num_rows, int num_experts);
 int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows, int num_experts,
@@ -116,11 +144,12 @@ int moe_routing_metadata_static(const int64_t* expert_idx, int64_t num_rows, int
 /* Same outputs from an existing exclusive prefix `group_indices` [E+1] (rows already in
  * expert order, identity permutation): used by the plain ragged grouped GEMM
  * (m_grouped_gemm with gather=scatter=False, triton_kernels/m_grouped_gemm.py:332-393).
- * row_src[p] is the unpadded row index. */
+ * row_src[p] is the unpadded row index.  A prefix that is not monotone from 0 to num_rows sets `status`
+ * (may be NULL) to 5; the offending segments get no rows. */
 int moe_layout_from_groups(const int32_t* group_indices, int64_t num_rows, int num_experts,
                            int32_t* pad_offsets, int32_t* row_src, int32_t* dst_row,
                            int32_t* mtile_expert, int32_t* tile_pairs, int32_t* num_mtiles,
-                           void* stream);
+                           int32_t* status, void* stream);
 
 /* ---------------------------------------------------------------------------------
  * Row movement (HBM-bound).  Replace row_gather / row_scatter
@@ -136,7 +165,7 @@ int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src,
 
 /* The layer's dispatch, token-major: dst[dst_row[t*topk + s], :] = src[t, :] for every token t and slot s
  * (each token row is read once and written topk times), padding rows (row_src[p] < 0, p < 128*num_mtiles)
- * are zeroed.  Same result as moe_gather_rows with div = topk. */
+ * are zeroed.  Same result as moe_gather_rows with div = topk.  Slots with dst_row < 0 are skipped. */
 int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* row_src,
                       const int32_t* num_mtiles, void* dst, int64_t num_tokens, int topk,
                       int64_t padded_rows, int cols, int dtype, void* stream);
@@ -147,14 +176,18 @@ int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* ro
  * rows are read with ordinary loads over NVLink.  scale (fp32, may be NULL) is applied in fp32.
  * chunk_count > 1 restricts the call to the rows of the experts [E*chunk_index/chunk_count,
  * E*(chunk_index+1)/chunk_count) (see moe_mgrouped_gemm); tile_pairs and num_experts are needed then.
+ * bulk_ctas > 0 selects the copy-engine kernel on that many CTAs (one per SM that is free for it): every warp
+ * moves whole rows with cp.async.bulk through a shared-memory slot, which keeps ~170 KB of remote reads in
+ * flight per SM; bulk_ctas == 0 selects the load/store kernel spread over all SMs.
  * No counterpart in the reference (it is single-GPU). */
 int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank,
                          const int32_t* src_row, const float* scale, const int32_t* num_mtiles,
                          const int32_t* tile_pairs, int num_experts, int chunk_index,
                          int chunk_count, void* dst, int64_t padded_rows, int cols, int dtype,
-                         void* stream);
+                         int bulk_ctas, int32_t* status, void* stream);
 
-/* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order. */
+/* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order (zeros where
+ * dst_row[j] < 0). */
 int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows,
                    int cols, int dtype, void* stream);
 
@@ -180,25 +213,84 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  * Requirements: every column count a multiple of 8; pointers 16-byte aligned.
  * --------------------------------------------------------------------------------- */
 
+/* Per-launch options of the grouped GEMMs (host struct; NULL or zeros = the library's choices).
+ *   max_ctas      cap on the CTAs of the launch (the kernels are persistent: a cap of sm_count - n leaves n SMs
+ *                 free for a kernel on another stream); 0 = one CTA per SM
+ *   wave_sync     0 = library's choice (on for K >= 8192), 1 = on, -1 = off: the persistent workers start each
+ *                 work item together, which keeps shared operand tiles in L2.  The barrier presumes all workers
+ *                 resident; a worker whose wait (~1 ms) runs out carries on unsynchronised and sets status 4
+ *   wave_workers  arrivals per wave the barrier waits for; 0 = the launch's worker count (anything larger can
+ *                 never be reached: the documented way to exercise the time-out path)
+ *   group_m       row units per scheduling group; 0 = default (12)
+ *   align_experts 0 = library's choice, 1 / -1 = scheduling groups never / may span two experts
+ *   single_cta    1 = one-SM kernels even when tile_pairs is given
+ *   wave_counter  device word for the barrier's arrivals, zeroed by the call on `stream`; NULL = a slot of the
+ *                 library's own ring (shared by all streams: a clash only costs a launch its barrier) */
+typedef struct moe_gemm_options {
+  int32_t max_ctas;
+  int32_t wave_sync;
+  int32_t wave_workers;
+  int32_t group_m;
+  int32_t align_experts;
+  int32_t single_cta;
+  uint32_t* wave_counter;
+} moe_gemm_options;
+
 /* M-grouped: out = epilogue(a[rows of tile] @ w[expert of tile]).
  *   mtile_expert / tile_pairs / num_mtiles come from moe_routing_metadata; tile_pairs may be
  *   NULL, which selects the one-SM-per-tile kernels instead of the paired-SM ones.
  *   padded_rows must be the moe_padded_rows_bound value the metadata was built with (the pair prefix is
- *   found at tile_pairs[padded_rows / 128]).
+ *   found at tile_pairs[padded_rows / 128]; a mismatch with num_mtiles[2] sets status 5 and computes nothing).
  *   chunk_count > 1 processes only the experts [E*chunk_index/chunk_count, E*(chunk_index+1)/chunk_count)
  *   (needs tile_pairs): a caller can run the row movement of chunk c+1 on another stream while the GEMMs
  *   of chunk c run.  chunk_count <= 1 processes everything.
  *   a    [RP, K]
  *   w    [E, K, N] when w_transposed == 0, [E, N, K] when w_transposed == 1
- *   act  MOE_ACT_NONE/SILU/GELU: out [RP, N];  MOE_ACT_SWIGLU/GEGLU: out [RP, N/2].
+ *   act  MOE_ACT_NONE/SILU/GELU/GELU_TANH: out [RP, N];  MOE_ACT_SWIGLU/GEGLU: out [RP, N/2].
  *        When pre_act != NULL (and act != MOE_ACT_NONE), pre_act [RP, N] receives the un-activated
  *        product, which moe_mgrouped_gemm_dglu needs in the backward pass. */
 int moe_mgrouped_gemm(const void* a, const void* w, void* out, void* pre_act,
                       const int32_t* mtile_expert, const int32_t* tile_pairs,
                       const int32_t* num_mtiles,
                       int64_t padded_rows, int K, int N, int num_experts, int w_transposed,
-                      int act, int dtype, int chunk_index, int chunk_count, int32_t* status,
-                      void* stream);
+                      int act, int dtype, int chunk_index, int chunk_count,
+                      const moe_gemm_options* options, int32_t* status, void* stream);
+
+/* The same contraction with the row gather fused into the operand loads (the GATHER_ROWS branch of the
+ * reference kernel, triton_kernels/m_grouped_gemm.py:104-109): padded row p reads row row_src[p] / div of
+ * src [src_rows, K] (zeros where row_src[p] < 0), fetched four rows at a time by tile::gather4 tensor copies;
+ * no [RP, K] copy of the rows exists.  w is [E, K, N].  src must be this GPU's own memory. */
+int moe_mgrouped_gemm_gather(const void* src, int64_t src_rows, const int32_t* row_src, int div,
+                             const void* w, void* out, void* pre_act, const int32_t* mtile_expert,
+                             const int32_t* tile_pairs, const int32_t* num_mtiles,
+                             int64_t padded_rows, int K, int N, int num_experts, int act, int dtype,
+                             const moe_gemm_options* options, int32_t* status, void* stream);
+
+/* The contraction with the top-k fold fused into the epilogue (the SCATTER_ROWS branch of the reference kernel,
+ * triton_kernels/m_grouped_gemm.py:168-172, plus functional/scale_and_reduce.py:3-5): accumulator row p
+ * (flat position j = row_src[p], skipped when negative) is multiplied by scores[j] (scale 1 when scores is NULL)
+ * and ADDED to row j / topk of out [T, N] with 16-byte vector reductions.  out must be zero when the call
+ * starts.  The k summands of a token are rounded to `dtype` one by one and arrive in no fixed order, so results
+ * are not bit-reproducible; moe_mgrouped_gemm + moe_combine_topk is the deterministic form. */
+int moe_mgrouped_gemm_combine(const void* a, const void* w, void* out, const int32_t* row_src,
+                              const void* scores, int topk, const int32_t* mtile_expert,
+                              const int32_t* tile_pairs, const int32_t* num_mtiles,
+                              int64_t padded_rows, int K, int N, int num_experts, int w_transposed,
+                              int dtype, const moe_gemm_options* options, int32_t* status,
+                              void* stream);
+
+/* The contraction with the row scatter fused into the epilogue (the SCATTER_ROWS branch of the reference kernel,
+ * triton_kernels/m_grouped_gemm.py:168-172): accumulator row p, after an optional element-wise activation
+ * (MOE_ACT_NONE/SILU/GELU/GELU_TANH), is stored at row out_rows[p] of out [*, N] (skipped when out_rows[p] < 0),
+ * whole 128-byte row segments per store.  The input rows may be gathered by the loads at the same time:
+ * a_row_src != NULL reads row a_row_src[p] / a_div of a [a_rows, K] (zeros where negative) as in
+ * moe_mgrouped_gemm_gather; a_row_src == NULL takes a as [RP, K] in the padded layout (a_rows, a_div ignored). */
+int moe_mgrouped_gemm_scatter(const void* a, int64_t a_rows, const int32_t* a_row_src, int a_div,
+                              const void* w, void* out, const int32_t* out_rows,
+                              const int32_t* mtile_expert, const int32_t* tile_pairs,
+                              const int32_t* num_mtiles, int64_t padded_rows, int K, int N,
+                              int num_experts, int w_transposed, int act, int dtype,
+                              const moe_gemm_options* options, int32_t* status, void* stream);
 
 /* Expert-parallel combine fused into the GEMM: the same contraction as moe_mgrouped_gemm without an
  * activation, but the epilogue stores accumulator row p at row dest_row[p] of the [*, N] matrix based at
@@ -211,34 +303,36 @@ int moe_mgrouped_gemm_push(const void* a, const void* w, void* const* peer_bases
                            const int32_t* mtile_expert, const int32_t* tile_pairs,
                            const int32_t* num_mtiles, int64_t padded_rows, int K, int N,
                            int num_experts, int w_transposed, int dtype, int chunk_index,
-                           int chunk_count, int32_t* status, void* stream);
+                           int chunk_count, const moe_gemm_options* options, int32_t* status,
+                           void* stream);
 
 /* Backward through the activation: d_pre = act'(pre_act) * (g[RP, K] @ w[E, N, K]^T),
  * i.e. for the layer: g = score-scaled dOut rows, w = weight2 [E, I, d] (N = I, K = d),
  * pre_act = the product saved by the forward GEMM.
  *   MOE_ACT_SWIGLU / MOE_ACT_GEGLU: pre_act and d_pre are [RP, 2N] (gate, up interleaved);
- *   MOE_ACT_SILU / MOE_ACT_GELU:    pre_act and d_pre are [RP, N].
+ *   MOE_ACT_SILU / MOE_ACT_GELU / MOE_ACT_GELU_TANH: pre_act and d_pre are [RP, N].
  * No counterpart in the reference (it has no backward). */
 int moe_mgrouped_gemm_dglu(const void* g, const void* w, const void* pre_act, void* d_pre,
                            const int32_t* mtile_expert, const int32_t* tile_pairs,
                            const int32_t* num_mtiles,
                            int64_t padded_rows, int K, int N, int num_experts, int act,
-                           int dtype, int chunk_index, int chunk_count, int32_t* status,
-                           void* stream);
-
-/* Process-wide cap on the number of CTAs of every grouped-GEMM launch that follows (0 = no cap, the
- * default: one CTA per SM).  The kernels are persistent, so a cap of sm_count - n leaves n SMs free for a
- * kernel on another stream; the expert-parallel path uses it while rows are pulled from peer GPUs, whose
- * loads crawl on SMs that share their L2 ingress with the GEMM's operand stream.  The value is read on the
- * host at launch time.  No counterpart in the reference. */
-int moe_set_gemm_grid_limit(int max_ctas);
+                           int dtype, int chunk_index, int chunk_count,
+                           const moe_gemm_options* options, int32_t* status, void* stream);
 
 /* K-grouped (expert weight gradients): dw[e] = a[rows of e]^T @ b[rows of e],
  *   a [RP, M], b [RP, N], dw [E, M, N]; experts without rows get zeros.
  * No counterpart in the reference (it has no backward). */
 int moe_kgrouped_gemm(const void* a, const void* b, void* dw, const int32_t* pad_offsets,
                       int64_t padded_rows, int M, int N, int num_experts, int dtype,
-                      int32_t* status, void* stream);
+                      const moe_gemm_options* options, int32_t* status, void* stream);
+
+/* The same with the rows of `a` gathered by the operand loads: padded row p contributes row row_src[p] / div
+ * of src [src_rows, M] (nothing where row_src[p] < 0).  Used for the gradient of weight1, whose `a` is the
+ * layer input in token order. */
+int moe_kgrouped_gemm_gather(const void* src, int64_t src_rows, const int32_t* row_src, int div,
+                             const void* b, void* dw, const int32_t* pad_offsets,
+                             int64_t padded_rows, int M, int N, int num_experts, int dtype,
+                             const moe_gemm_options* options, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -4,7 +4,12 @@
 
 #include <string.h>
 
+#include <atomic>
+
 namespace moe {
+
+static std::atomic<long long> g_wait_limit{kDefaultWaitLimitCycles};
+long long wait_limit_cycles() { return g_wait_limit.load(std::memory_order_relaxed); }
 
 static thread_local char g_error[512] = "";
 
@@ -64,10 +69,35 @@ extern "C" int moe_check_status(const int32_t* status, void* stream) {
   MOE_CUDA(cudaMemcpyAsync(&host, status, sizeof(host), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
   MOE_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
   if (host == 0) return MOE_OK;
-  if (host == 100) {
+  if (host == DS_BAD_EXPERT_ID) {
     set_error("routing metadata saw an expert id outside [0, num_experts); such rows were dropped");
     return MOE_ERR_INVALID;
   }
-  set_error("a device-side bounded wait ran out (code %d: 1 = TMA producer, 2 = MMA issuer, 3 = epilogue)", host);
+  if (host == DS_BAD_LAYOUT) {
+    set_error("routing metadata does not describe the rows it was used with (a group prefix that is not a prefix of "
+              "num_rows, or padded_rows differing from the bound the metadata was built with)");
+    return MOE_ERR_INVALID;
+  }
+  if (host == DS_WAVE_FALLBACK) {
+    set_error("the wave barrier of a grouped GEMM ran out (its workers were not all resident); that launch finished "
+              "with unsynchronised scheduling and its results are valid");
+    return MOE_ERR_TIMEOUT;
+  }
+  set_error("a device-side bounded wait ran out (code %d: 1 = TMA producer, 2 = MMA issuer, 3 = epilogue); the outputs "
+            "of that launch are incomplete", host);
   return MOE_ERR_TIMEOUT;
+}
+
+extern "C" int moe_read_status(const int32_t* status, int32_t* code, int reset, void* stream) {
+  MOE_CHECK_ARG(status != nullptr && code != nullptr, "moe_read_status: null pointer argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  MOE_CUDA(cudaMemcpyAsync(code, status, sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+  if (reset) MOE_CUDA(cudaMemsetAsync(const_cast<int32_t*>(status), 0, sizeof(int32_t), s));
+  MOE_CUDA(cudaStreamSynchronize(s));
+  return MOE_OK;
+}
+
+extern "C" int moe_set_wait_limit_cycles(int64_t cycles) {
+  g_wait_limit.store(cycles > 0 ? cycles : kDefaultWaitLimitCycles, std::memory_order_relaxed);
+  return MOE_OK;
 }

@@ -46,7 +46,14 @@ enum DeviceStatus : int {
   DS_TIMEOUT_PRODUCER = 1,  // TMA producer gave up waiting for a free shared-memory stage
   DS_TIMEOUT_MMA = 2,       // MMA issuer gave up waiting for operands or a free accumulator
   DS_TIMEOUT_EPILOGUE = 3,  // epilogue gave up waiting for an accumulator
+  DS_WAVE_FALLBACK = 4,     // the wave barrier of the persistent workers ran out; the launch finished with the static
+                            // stride instead (its results are valid)
+  DS_BAD_LAYOUT = 5,        // the routing metadata handed to a kernel was built for another padded row count
+  DS_BAD_EXPERT_ID = 100,   // routing metadata saw an expert id outside [0, num_experts); the row was dropped
 };
+
+// Limit (in SM clock cycles) of every device-side wait of the launches that follow; see moe_set_wait_limit_cycles.
+long long wait_limit_cycles();
 
 // ----------------------------------------------------------------------------------
 // device side: element types
@@ -135,23 +142,34 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in this library is bounded: after kWaitLimitCycles the waiter raises the
-// CTA-wide abort flag, records why in the caller's status word and returns false.  All
-// other waiters see the flag and give up too, so the kernel always terminates.
-constexpr long long kWaitLimitCycles = 1ll << 32;  // ~2 s at B200 clocks
+// Every wait in this library is bounded: after `limit` clock cycles the waiter raises the abort flag of its
+// CTA (and of the other CTA of its pair), records why in the caller's status word and returns false.  All
+// other waiters see the flag and give up too, so the kernel always terminates by itself.
+constexpr long long kDefaultWaitLimitCycles = 1ll << 32;  // ~2 s at B200 clocks
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+struct WaitCtx {
+  volatile int* abort_flag;  // this CTA's flag (shared memory)
+  uint32_t peer_abort;       // shared::cluster address of the flag of the other CTA of the pair; 0 without a pair
+  int* status;               // caller's status word (may be null)
+  long long limit;           // cycles
+};
+
+__device__ __forceinline__ void raise_abort(const WaitCtx& w, int code) {
+  *w.abort_flag = 1;
+  if (w.peer_abort != 0) asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(w.peer_abort), "r"(1) : "memory");
+  if (w.status != nullptr) atomicCAS(w.status, 0, code);
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& w, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   int spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if (((++spins) & 63) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
-        *abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
+      if (*w.abort_flag) return false;
+      if (clock64() - t0 > w.limit) {
+        raise_abort(w, code);
         return false;
       }
     }
@@ -159,21 +177,11 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // TMA tile loads (no cluster qualifiers anywhere: every CTA fetches its own tiles).
-// L2 eviction-priority policies for the tile loads: operand tiles that are re-read many times (the row
-// tiles, swept over every column tile) are kept, tiles that stream through once (expert weights) go first.
-__device__ __forceinline__ uint64_t l2_policy_evict_last() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
+// L2 policy handed to the tile loads (normal priority: marking weight tiles evict-first made CTA pairs that share a
+// weight tile miss it, measured +50 % DRAM reads).
 __device__ __forceinline__ uint64_t l2_policy_evict_normal() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
-  return p;
-}
-__device__ __forceinline__ uint64_t l2_policy_evict_first() {
-  uint64_t p;
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar,
@@ -195,6 +203,47 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
+
+// Four rows of a 2-D tensor gathered by row index into four consecutive 128-byte shared-memory rows (tensor map
+// with a {64, 1} box and the 128-byte swizzle).  Rows outside the tensor read as zeros.  c0 (elements) must be a
+// multiple of 8.  Any number of lanes of a warp may issue one of these each.
+__device__ __forceinline__ void tma_gather4(uint32_t dst, const CUtensorMap* map, int c0, const int4& rows, uint32_t bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::1.L2::cache_hint "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w), "r"(bar), "l"(policy)
+      : "memory");
+}
+// The same issued by either CTA of a pair, the bytes credited to `bar` in the shared::cluster window.
+__device__ __forceinline__ void tma_gather4_pair(uint32_t dst, const CUtensorMap* map, int c0, const int4& rows,
+                                                 uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes.cta_group::2.L2::cache_hint "
+      "[%0], [%1, {%2, %3, %4, %5, %6}], [%7], %8;"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(rows.x), "r"(rows.y), "r"(rows.z), "r"(rows.w), "r"(bar), "l"(policy)
+      : "memory");
+}
+// Plain 2-D tile load without a cache hint (epilogue side inputs).
+__device__ __forceinline__ void tma_load_2d_plain(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cta.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar)
+      : "memory");
+}
+// 2-D tile store from shared memory (bulk async-group completion); parts of the box outside the tensor are dropped.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until the bulk stores committed by this thread have finished READING shared memory (the buffer may be reused).
+__device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// Wait until the bulk stores committed by this thread are complete.
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// Orders this thread's generic-proxy shared-memory writes before later async-proxy (TMA) reads of them.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // TMEM allocation (whole warp executes these).
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_slot, uint32_t ncols) {
@@ -318,10 +367,14 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&v)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// 16-byte global store with the streaming (evict-first) cache policy: GEMM outputs are written once and
-// not re-read by the kernel that writes them, so they should not displace operand tiles in L2.
-__device__ __forceinline__ void st_global_stream(void* ptr, const uint4& v) {
-  asm volatile("st.global.cs.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+// 16 bytes (eight 16-bit values) added to global memory element-wise, no return value.
+template <typename T> __device__ __forceinline__ void red_add_v8(void* ptr, const uint4& v);
+template <> __device__ __forceinline__ void red_add_v8<__nv_bfloat16>(void* ptr, const uint4& v) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+template <> __device__ __forceinline__ void red_add_v8<__half>(void* ptr, const uint4& v) {
+  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(ptr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
                : "memory");
 }
 
@@ -329,6 +382,17 @@ __device__ __forceinline__ void st_global_stream(void* ptr, const uint4& v) {
 __device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
 __device__ __forceinline__ float silu_f(float x) { return x * sigmoidf_fast(x); }
 __device__ __forceinline__ float gelu_f(float x) { return 0.5f * x * (1.0f + erff(x * 0.70710678118654752f)); }
+// tanh form: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+__device__ __forceinline__ float gelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  return 0.5f * x * (1.0f + tanhf(u));
+}
+__device__ __forceinline__ float dgelu_tanh_f(float x) {
+  const float u = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+  const float t = tanhf(u);
+  const float du = 0.7978845608028654f * (1.0f + 3.0f * 0.044715f * x * x);
+  return 0.5f * (1.0f + t) + 0.5f * x * (1.0f - t * t) * du;
+}
 __device__ __forceinline__ float dsilu_f(float x) {
   float s = sigmoidf_fast(x);
   return s * (1.0f + x * (1.0f - s));

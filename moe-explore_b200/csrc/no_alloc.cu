@@ -20,6 +20,8 @@
 //     cudaGetSymbolAddress, no allocation); make that first call outside any stream capture.
 #include "common.cuh"
 
+#include <atomic>
+
 namespace {
 
 constexpr size_t kStaticScratchBytes = 1u << 20;
@@ -29,7 +31,9 @@ static __device__ __align__(256) unsigned char g_routing_scratch[kStaticScratchB
 
 // Device address of g_routing_scratch on each device.  In host code the symbol's name is only a
 // handle: the address a kernel can use has to be asked for, per device, with that device current.
-void* g_scratch_ptr[kMaxDevices] = {};
+// Atomic slots: two host threads making a device's first call together both look the address up
+// and store the same value.
+std::atomic<void*> g_scratch_ptr[kMaxDevices];
 
 int scratch_for_current_device(void** out) {
   int dev = -1;
@@ -39,12 +43,12 @@ int scratch_for_current_device(void** out) {
                    kMaxDevices);
     return MOE_ERR_UNSUPPORTED;
   }
-  if (g_scratch_ptr[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = g_scratch_ptr[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     MOE_CUDA(cudaGetSymbolAddress(&p, g_routing_scratch));
-    g_scratch_ptr[dev] = p;
+    g_scratch_ptr[dev].store(p, std::memory_order_release);
   }
-  *out = g_scratch_ptr[dev];
+  *out = p;
   return MOE_OK;
 }
 

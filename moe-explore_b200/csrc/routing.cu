@@ -6,9 +6,10 @@
 // three-kernel counting sort (the number of distinct keys, E, is small):
 //   1. chunk_histogram : each warp owns a contiguous chunk of kChunk flat positions and counts
 //                        its ids per expert in shared memory (warp-aggregated via match.any);
-//   2. scan_offsets    : one CTA turns the [chunks, E] histogram into per-(chunk, expert)
-//                        exclusive offsets, the per-expert prefix sums (unpadded and padded to
-//                        128-row tiles) and the tile -> expert map;
+//   2. scan_offsets    : turns the [chunks, E] histogram into per-(chunk, expert) exclusive
+//                        offsets (one CTA per expert scans down the chunk axis when there are many
+//                        chunks), then one CTA derives the per-expert prefix sums (unpadded and
+//                        padded to 128-row tiles) and the tile -> expert map;
 //   3. place_rows      : each warp walks its chunk again in order, ranks equal ids with
 //                        match.any + popc (which preserves flat-position order) and writes
 //                        perm / row_src / dst_row.
@@ -46,7 +47,7 @@ __device__ __forceinline__ void load_keys(const int64_t* __restrict__ ids, int64
     bad |= (j < R) && !ok;
     keys[i] = ok ? static_cast<int>(raw[i]) : -1 - lane;
   }
-  if (bad && status != nullptr) atomicCAS(status, 0, 100);  // id out of range: dropped from every output
+  if (bad && status != nullptr) atomicCAS(status, 0, DS_BAD_EXPERT_ID);  // id out of range: dropped from every output
 }
 
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
@@ -91,28 +92,73 @@ __device__ __forceinline__ void write_tile_maps(int e, int32_t row_begin, int32_
   }
 }
 
-// One CTA, one thread per expert (E <= 1024).
+// Many chunks: one CTA per expert turns its column of the [chunks, E] histogram into exclusive offsets (every
+// thread owns a contiguous run of chunks; block-wide scan of the run sums) and leaves the expert's row count in
+// group_indices[e + 1] for the single-CTA pass below.
+constexpr int kScanThreads = 256;
+__global__ void __launch_bounds__(kScanThreads)
+scan_chunks_kernel(const int32_t* __restrict__ chunk_hist, int32_t* __restrict__ chunk_off, int64_t nchunks, int E,
+                   int32_t* __restrict__ group_indices) {
+  __shared__ int32_t warp_sum[kScanThreads / 32];
+  const int e = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t per = (nchunks + kScanThreads - 1) / kScanThreads;
+  const int64_t c0 = tid * per;
+  const int64_t c1 = c0 + per < nchunks ? c0 + per : nchunks;
+  int32_t mine = 0;
+  for (int64_t c = c0; c < c1; ++c) mine += chunk_hist[c * E + e];
+  int32_t incl = mine;
+#pragma unroll
+  for (int off = 1; off < 32; off <<= 1) {
+    const int32_t v = __shfl_up_sync(0xFFFFFFFFu, incl, off);
+    if (lane >= off) incl += v;
+  }
+  if (lane == 31) warp_sum[warp] = incl;
+  __syncthreads();
+  int32_t before = 0, total = 0;
+#pragma unroll
+  for (int w = 0; w < kScanThreads / 32; ++w) {
+    if (w < warp) before += warp_sum[w];
+    total += warp_sum[w];
+  }
+  int32_t run = before + incl - mine;
+  for (int64_t c = c0; c < c1; ++c) {
+    chunk_off[c * E + e] = run;
+    run += chunk_hist[c * E + e];
+  }
+  if (tid == 0) group_indices[e + 1] = total;
+}
+
+// One CTA, one thread per expert (E <= 1024).  `counts_ready`: the per-expert row counts are already in
+// group_indices[1..E] (scan_chunks_kernel ran); otherwise this kernel scans the chunk axis itself (few chunks).
+// num_mtiles receives {tiles in use, tile pairs in use, mtiles_bound, 0}; perm entries past the rows that were
+// kept (ids out of range are dropped) are set to -1.
 __global__ void __launch_bounds__(kMaxExperts)
 scan_offsets_kernel(const int32_t* __restrict__ chunk_hist, int32_t* __restrict__ chunk_off, int64_t nchunks, int E,
-                    int32_t* __restrict__ group_indices,
+                    int counts_ready, int32_t* __restrict__ group_indices,
                     int32_t* __restrict__ pad_offsets, int32_t* __restrict__ mtile_expert,
-                    int32_t* __restrict__ tile_pairs, int32_t* __restrict__ num_mtiles, int mtiles_bound) {
+                    int32_t* __restrict__ tile_pairs, int32_t* __restrict__ num_mtiles, int mtiles_bound,
+                    int64_t* __restrict__ perm, int64_t R) {
   __shared__ int32_t sh_a[kMaxExperts];
   __shared__ int32_t sh_b[kMaxExperts];
   __shared__ int32_t sh_c[kMaxExperts];
   const int e = threadIdx.x;
   int32_t total = 0;
   if (e < E) {
-    // exclusive scan down the chunk axis for this expert
-    constexpr int kBatch = 16;  // loads in flight per thread
-    for (int64_t c0 = 0; c0 < nchunks; c0 += kBatch) {
-      int32_t v[kBatch];
+    if (counts_ready) {
+      total = group_indices[e + 1];
+    } else {
+      // exclusive scan down the chunk axis for this expert
+      constexpr int kBatch = 16;  // loads in flight per thread
+      for (int64_t c0 = 0; c0 < nchunks; c0 += kBatch) {
+        int32_t v[kBatch];
 #pragma unroll
-      for (int i = 0; i < kBatch; ++i) v[i] = (c0 + i < nchunks) ? chunk_hist[(c0 + i) * E + e] : 0;
+        for (int i = 0; i < kBatch; ++i) v[i] = (c0 + i < nchunks) ? chunk_hist[(c0 + i) * E + e] : 0;
 #pragma unroll
-      for (int i = 0; i < kBatch; ++i) {
-        if (c0 + i < nchunks) chunk_off[(c0 + i) * E + e] = total;
-        total += v[i];
+        for (int i = 0; i < kBatch; ++i) {
+          if (c0 + i < nchunks) chunk_off[(c0 + i) * E + e] = total;
+          total += v[i];
+        }
       }
     }
   }
@@ -141,8 +187,14 @@ scan_offsets_kernel(const int32_t* __restrict__ chunk_hist, int32_t* __restrict_
     if (num_mtiles != nullptr && e == E - 1) {
       num_mtiles[0] = sh_b[e] / MOE_TILE_M;
       num_mtiles[1] = sh_c[e];
+      num_mtiles[2] = mtiles_bound;
+      num_mtiles[3] = 0;
       if (pair_prefix != nullptr) pair_prefix[E] = sh_c[e];
     }
+  }
+  if (perm != nullptr) {
+    const int64_t kept = sh_a[E - 1];
+    for (int64_t r = kept + threadIdx.x; r < R; r += kMaxExperts) perm[r] = -1;
   }
 }
 
@@ -176,6 +228,8 @@ place_rows_kernel(const int64_t* __restrict__ ids, int64_t R, int E, const int32
       const int32_t p = pad_offsets[key] + rank;
       if (row_src != nullptr) row_src[p] = static_cast<int32_t>(j);
       if (dst_row != nullptr) dst_row[j] = p;
+    } else if (j < R && dst_row != nullptr) {
+      dst_row[j] = -1;  // id out of range: the row is in no expert's segment; consumers skip negative rows
     }
   }
 }
@@ -185,13 +239,18 @@ place_rows_kernel(const int64_t* __restrict__ ids, int64_t R, int E, const int32
 __global__ void __launch_bounds__(kMaxExperts)
 layout_from_groups_kernel(const int32_t* __restrict__ group_indices, int64_t R, int E, int32_t* __restrict__ pad_offsets,
                           int32_t* __restrict__ mtile_expert, int32_t* __restrict__ tile_pairs,
-                          int32_t* __restrict__ num_mtiles, int mtiles_bound) {
+                          int32_t* __restrict__ num_mtiles, int mtiles_bound, int32_t* status) {
   __shared__ int32_t sh_b[kMaxExperts];
   __shared__ int32_t sh_c[kMaxExperts];
   const int e = threadIdx.x;
   int32_t padded = 0;
   if (e < E) {
-    const int32_t cnt = group_indices[e + 1] - group_indices[e];
+    // a prefix that is not monotone, does not start at 0 or does not end at R describes no layout: such experts
+    // get no rows here and the status word says so
+    const int32_t lo = group_indices[e], hi = group_indices[e + 1];
+    const bool bad = hi < lo || lo < 0 || hi > R || (e == 0 && lo != 0) || (e == E - 1 && hi != R);
+    if (bad && status != nullptr) atomicCAS(status, 0, DS_BAD_LAYOUT);
+    const int32_t cnt = bad ? 0 : hi - lo;
     padded = (cnt + MOE_TILE_M - 1) / MOE_TILE_M * MOE_TILE_M;
   }
   const int32_t pairs = (padded / MOE_TILE_M + 1) / 2;
@@ -214,6 +273,8 @@ layout_from_groups_kernel(const int32_t* __restrict__ group_indices, int64_t R, 
     if (num_mtiles != nullptr && e == E - 1) {
       num_mtiles[0] = sh_b[e] / MOE_TILE_M;
       num_mtiles[1] = sh_c[e];
+      num_mtiles[2] = mtiles_bound;
+      num_mtiles[3] = 0;
       if (pair_prefix != nullptr) pair_prefix[E] = sh_c[e];
     }
   }
@@ -229,8 +290,11 @@ __global__ void layout_rows_kernel(const int32_t* __restrict__ group_indices, co
     const int mid = (lo + hi) >> 1;
     if (group_indices[mid] <= j) lo = mid; else hi = mid;
   }
-  const int32_t p = pad_offsets[lo] + static_cast<int32_t>(j - group_indices[lo]);
-  if (row_src != nullptr) row_src[p] = static_cast<int32_t>(j);
+  // rows of a segment the layout kernel refused (bad prefix) have no padded row
+  const int64_t in_seg = j - group_indices[lo];
+  const bool ok = in_seg >= 0 && in_seg < pad_offsets[lo + 1] - pad_offsets[lo] && j < group_indices[lo + 1];
+  const int32_t p = ok ? pad_offsets[lo] + static_cast<int32_t>(in_seg) : -1;
+  if (ok && row_src != nullptr) row_src[p] = static_cast<int32_t>(j);
   if (dst_row != nullptr) dst_row[j] = p;
 }
 
@@ -291,9 +355,15 @@ extern "C" int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows,
     chunk_histogram_kernel<<<blocks, kWarpsPerBlock * 32, sh, s>>>(expert_idx, num_rows, num_experts, chunk_hist, status);
     MOE_CUDA(cudaGetLastError());
   }
-  scan_offsets_kernel<<<1, kMaxExperts, 0, s>>>(chunk_hist, chunk_off, chunks, num_experts, group_indices, pad_offsets,
-                                               mtile_expert, tile_pairs, num_mtiles,
-                                               static_cast<int>(moe_mtiles_bound(num_rows, num_experts)));
+  // many chunks: scan the chunk axis with one CTA per expert first (a single CTA walking 512 chunks took 53 us)
+  const int split_scan = chunks > 64 ? 1 : 0;
+  if (split_scan) {
+    scan_chunks_kernel<<<num_experts, kScanThreads, 0, s>>>(chunk_hist, chunk_off, chunks, num_experts, group_indices);
+    MOE_CUDA(cudaGetLastError());
+  }
+  scan_offsets_kernel<<<1, kMaxExperts, 0, s>>>(chunk_hist, chunk_off, chunks, num_experts, split_scan, group_indices,
+                                               pad_offsets, mtile_expert, tile_pairs, num_mtiles,
+                                               static_cast<int>(moe_mtiles_bound(num_rows, num_experts)), perm, num_rows);
   MOE_CUDA(cudaGetLastError());
   if (chunks > 0 && (perm || row_src || dst_row)) {
     place_rows_kernel<<<blocks, kWarpsPerBlock * 32, sh, s>>>(expert_idx, num_rows, num_experts, chunk_off,
@@ -305,7 +375,7 @@ extern "C" int moe_routing_metadata(const int64_t* expert_idx, int64_t num_rows,
 
 extern "C" int moe_layout_from_groups(const int32_t* group_indices, int64_t num_rows, int num_experts,
                                       int32_t* pad_offsets, int32_t* row_src, int32_t* dst_row, int32_t* mtile_expert,
-                                      int32_t* tile_pairs, int32_t* num_mtiles, void* stream) {
+                                      int32_t* tile_pairs, int32_t* num_mtiles, int32_t* status, void* stream) {
   MOE_CHECK_ARG(group_indices && pad_offsets, "moe_layout_from_groups: group_indices and pad_offsets are required");
   MOE_CHECK_ARG(num_rows >= 0 && num_experts > 0, "moe_layout_from_groups: bad sizes R=%lld E=%d", (long long)num_rows,
                 num_experts);
@@ -323,7 +393,7 @@ extern "C" int moe_layout_from_groups(const int32_t* group_indices, int64_t num_
   }
   layout_from_groups_kernel<<<1, kMaxExperts, 0, s>>>(group_indices, num_rows, num_experts, pad_offsets, mtile_expert,
                                                      tile_pairs, num_mtiles,
-                                                     static_cast<int>(moe_mtiles_bound(num_rows, num_experts)));
+                                                     static_cast<int>(moe_mtiles_bound(num_rows, num_experts)), status);
   MOE_CUDA(cudaGetLastError());
   if (num_rows > 0 && (row_src || dst_row)) {
     const int threads = 256;

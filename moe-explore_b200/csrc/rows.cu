@@ -7,8 +7,6 @@
 // and scale_and_reduce (src/moe_explore/functional/scale_and_reduce.py:3-5).
 #include "common.cuh"
 
-#include <stdlib.h>
-
 namespace moe {
 
 constexpr int kRowThreads = 256;
@@ -44,7 +42,10 @@ dispatch_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ 
       const int32_t* rows = dst_row + t * topk;
       for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) {
         const uint4 u = s[v];
-        for (int k = 0; k < topk; ++k) dst[static_cast<int64_t>(rows[k]) * vec_per_row + v] = u;
+        for (int k = 0; k < topk; ++k) {
+          const int32_t p = rows[k];  // negative: the routing metadata dropped this (token, slot)
+          if (p >= 0) dst[static_cast<int64_t>(p) * vec_per_row + v] = u;
+        }
       }
     }
   } else {
@@ -61,6 +62,27 @@ dispatch_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ 
   }
 }
 
+// Row window of a pull: everything, or the rows of the experts of chunk `chunk_index` of `chunk_count` (the same
+// slicing the grouped GEMMs use, so a caller can pipeline the pull of chunk c+1 against the GEMMs of chunk c).
+// False when the metadata was built for another padded row count.
+__device__ __forceinline__ bool peer_row_window(const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
+                                                int num_experts, int mtiles_bound, int chunk_index, int chunk_count,
+                                                int64_t& row_begin, int64_t& row_end) {
+  row_begin = 0;
+  row_end = static_cast<int64_t>(num_mtiles[0]) * MOE_TILE_M;
+  if (chunk_count > 1) {
+    if (num_mtiles[2] != mtiles_bound) return false;
+    const int32_t* pair_prefix = tile_pairs + mtiles_bound;
+    const int pairs = num_mtiles[1];
+    const int e0 = static_cast<int>(static_cast<long long>(num_experts) * chunk_index / chunk_count);
+    const int e1 = static_cast<int>(static_cast<long long>(num_experts) * (chunk_index + 1) / chunk_count);
+    const int p0 = pair_prefix[e0], p1 = pair_prefix[e1];
+    if (p1 < pairs) row_end = static_cast<int64_t>(tile_pairs[p1] & 0xFFFFF) * MOE_TILE_M;
+    row_begin = p0 < pairs ? static_cast<int64_t>(tile_pairs[p0] & 0xFFFFF) * MOE_TILE_M : row_end;
+  }
+  return true;
+}
+
 // dst[p, :] = scale[p] * bases[src_rank[p]][src_row[p], :], zeros where src_rank[p] < 0.  `bases` holds
 // one base pointer per rank of the node: the source rows live in peers' memory and are read with
 // ordinary 16-byte loads over NVLink (this GPU's own rows through the same path).
@@ -71,19 +93,8 @@ gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* _
                         const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
                         int num_experts, int mtiles_bound, int chunk_index, int chunk_count, uint4* __restrict__ dst,
                         int vec_per_row) {
-  // Row window: everything, or the rows of the experts of chunk `chunk_index` of `chunk_count` (the same slicing
-  // the grouped GEMMs use, so a caller can pipeline the pull of chunk c+1 against the GEMMs of chunk c).
-  int64_t row_begin = 0;
-  int64_t row_end = static_cast<int64_t>(num_mtiles[0]) * MOE_TILE_M;
-  if (chunk_count > 1) {
-    const int32_t* pair_prefix = tile_pairs + mtiles_bound;
-    const int pairs = num_mtiles[1];
-    const int e0 = static_cast<int>(static_cast<long long>(num_experts) * chunk_index / chunk_count);
-    const int e1 = static_cast<int>(static_cast<long long>(num_experts) * (chunk_index + 1) / chunk_count);
-    const int p0 = pair_prefix[e0], p1 = pair_prefix[e1];
-    if (p1 < pairs) row_end = static_cast<int64_t>(tile_pairs[p1] & 0xFFFFF) * MOE_TILE_M;
-    row_begin = p0 < pairs ? static_cast<int64_t>(tile_pairs[p0] & 0xFFFFF) * MOE_TILE_M : row_end;
-  }
+  int64_t row_begin, row_end;
+  if (!peer_row_window(num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count, row_begin, row_end)) return;
   for (int64_t p = row_begin + blockIdx.x; p < row_end; p += gridDim.x) {
     const int32_t r = src_rank[p];
     uint4* d = dst + p * vec_per_row;
@@ -122,13 +133,103 @@ gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* _
   }
 }
 
+// The same pull with the copy engine of the SM doing the moving: every warp owns one shared-memory slot of one
+// row; one lane fetches the row with a bulk asynchronous copy (global -> shared, completion on an mbarrier), the
+// warp scales it in place when asked to, and one lane sends it on with a bulk copy shared -> global.  A row of
+// 14 KB is in flight per warp without a register holding any of it, so a CTA keeps ~170 KB of remote reads
+// outstanding -- what a pull over NVLink (microseconds of latency) needs when it has only a few SMs to itself.
+// Launched with at most as many CTAs as there are SMs free for it (one CTA per SM: the slots take the shared memory).
+constexpr int kBulkMaxWarps = 16;
+template <typename T>
+__global__ void __launch_bounds__(kBulkMaxWarps * 32)
+pull_rows_bulk_kernel(const uint4* const* __restrict__ bases, const int32_t* __restrict__ src_rank,
+                      const int32_t* __restrict__ src_row, const float* __restrict__ scale,
+                      const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs, int num_experts,
+                      int mtiles_bound, int chunk_index, int chunk_count, uint4* __restrict__ dst, int vec_per_row,
+                      long long wait_limit, int32_t* status) {
+  extern __shared__ __align__(128) uint8_t slots_raw[];
+  __shared__ __align__(8) uint64_t bars[kBulkMaxWarps];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  const uint32_t row_bytes = static_cast<uint32_t>(vec_per_row) * 16u;
+  const uint32_t slot = smem_u32(slots_raw) + warp * row_bytes;
+  uint4* slot_ptr = reinterpret_cast<uint4*>(slots_raw + static_cast<size_t>(warp) * row_bytes);
+  const uint32_t bar = smem_u32(&bars[warp]);
+  if (lane == 0) {
+    mbar_init(bar, 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  int64_t row_begin, row_end;
+  if (!peer_row_window(num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count, row_begin, row_end)) return;
+  uint32_t phase = 0;
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * warps;
+  for (int64_t p = row_begin + static_cast<int64_t>(blockIdx.x) * warps + warp; p < row_end; p += stride) {
+    const int32_t r = src_rank[p];
+    uint4* d = dst + p * vec_per_row;
+    if (r < 0) {
+      for (int v = lane; v < vec_per_row; v += 32) d[v] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const uint4* src = bases[r] + static_cast<int64_t>(src_row[p]) * vec_per_row;
+    if (lane == 0) {
+      bulk_wait_read_all();  // the store of this warp's previous row has left the slot
+      mbar_arrive_expect_tx(bar, row_bytes);
+      asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(slot), "l"(src), "r"(row_bytes), "r"(bar)
+                   : "memory");
+    }
+    __syncwarp();
+    // bounded wait for the row
+    bool arrived = mbar_try_wait(bar, phase);
+    if (!arrived) {
+      const long long t0 = clock64();
+      while (!(arrived = mbar_try_wait(bar, phase))) {
+        if (clock64() - t0 > wait_limit) break;
+      }
+    }
+    if (!__all_sync(0xFFFFFFFFu, arrived)) {
+      if (lane == 0 && status != nullptr) atomicCAS(status, 0, DS_TIMEOUT_PRODUCER);
+      for (int i = 0; i < 2000; ++i) __nanosleep(1000);  // let the copy land before the CTA gives up its shared memory
+      break;
+    }
+    phase ^= 1;
+    if (scale != nullptr) {
+      const float f = scale[p];
+      for (int v = lane; v < vec_per_row; v += 32) {
+        const uint4 u = slot_ptr[v];
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 x = Elem<T>::unpack2(w[k]);
+          o[k] = Elem<T>::pack2(f * x.x, f * x.y);
+        }
+        slot_ptr[v] = make_uint4(o[0], o[1], o[2], o[3]);
+      }
+      fence_proxy_async_smem();
+    }
+    __syncwarp();
+    if (lane == 0) {
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(d), "r"(slot), "r"(row_bytes) : "memory");
+      bulk_commit();
+    }
+  }
+  if (lane == 0) bulk_wait_all();
+}
+
 // out[j, :] = src[dst_row[j], :]
 __global__ void __launch_bounds__(kRowThreads)
 unpad_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ dst_row, uint4* __restrict__ out,
                   int64_t num_rows, int vec_per_row) {
   for (int64_t j = blockIdx.x; j < num_rows; j += gridDim.x) {
-    const uint4* s = src + static_cast<int64_t>(dst_row[j]) * vec_per_row;
+    const int32_t p = dst_row[j];
     uint4* d = out + j * vec_per_row;
+    if (p < 0) {  // no source row (dropped by the routing metadata): zeros
+      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = make_uint4(0, 0, 0, 0);
+      continue;
+    }
+    const uint4* s = src + static_cast<int64_t>(p) * vec_per_row;
     for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = s[v];
   }
 }
@@ -154,8 +255,10 @@ combine_topk_kernel(const uint4* __restrict__ ys, const T* __restrict__ scores, 
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int s = 0; s < topk; ++s) {
         const int64_t j = t * topk + s;
+        const int32_t p = dst_row[j];
+        if (p < 0) continue;  // slot dropped by the routing metadata: contributes nothing
         const float scale = scores != nullptr ? Elem<T>::to_float(scores[j]) : 1.0f;
-        const uint4 u = ys[static_cast<int64_t>(dst_row[j]) * vec_per_row + v];
+        const uint4 u = ys[static_cast<int64_t>(p) * vec_per_row + v];
         fma8<T>(acc, u, scale);
       }
       uint4 r;
@@ -263,7 +366,8 @@ extern "C" int moe_dispatch_rows(const void* src, const int32_t* dst_row, const 
 extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank, const int32_t* src_row,
                                     const float* scale, const int32_t* num_mtiles, const int32_t* tile_pairs,
                                     int num_experts, int chunk_index, int chunk_count, void* dst,
-                                    int64_t padded_rows, int cols, int dtype, void* stream) {
+                                    int64_t padded_rows, int cols, int dtype, int bulk_ctas, int32_t* status,
+                                    void* stream) {
   MOE_CHECK_ARG(peer_bases && src_rank && src_row && num_mtiles && dst, "moe_gather_rows_peer: null pointer argument");
   MOE_CHECK_ARG(aligned16(dst), "moe_gather_rows_peer: dst must be 16-byte aligned");
   MOE_CHECK_ARG(padded_rows > 0, "moe_gather_rows_peer: bad sizes");
@@ -273,16 +377,35 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
   const int mtiles_bound = static_cast<int>(padded_rows / MOE_TILE_M);
   MOE_ROW_COMMON_CHECKS("moe_gather_rows_peer", cols, dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  // This kernel is bound by NVLink, not by SMs, and usually runs beside a grouped GEMM: a few CTAs per SM keep the
-  // links busy without taking issue slots from the GEMM (MOE_SM100_PEER_GATHER_CTAS overrides, for measurements).
-  static int ctas_per_sm = 0;
-  if (ctas_per_sm == 0) {
-    const char* v = getenv("MOE_SM100_PEER_GATHER_CTAS");
-    ctas_per_sm = v != nullptr && atoi(v) > 0 ? atoi(v) : 4;
-  }
-  const int64_t cap = static_cast<int64_t>(sm_count()) * ctas_per_sm;
-  const int grid = static_cast<int>(padded_rows < cap ? padded_rows : cap);
   const uint4* const* bases = reinterpret_cast<const uint4* const*>(peer_bases);
+  if (bulk_ctas > 0) {
+    // copy-engine variant: one row slot per warp, as many warps as 200 KB of shared memory hold (4..16)
+    const size_t row_bytes = static_cast<size_t>(cols) * 2;
+    int warps = static_cast<int>((200 * 1024) / row_bytes);
+    if (warps > kBulkMaxWarps) warps = kBulkMaxWarps;
+    if (warps >= 4) {
+      const size_t smem = row_bytes * warps;
+      const int grid_b = bulk_ctas < sm_count() ? bulk_ctas : sm_count();
+      if (dtype == MOE_DTYPE_BF16) {
+        MOE_CUDA(cudaFuncSetAttribute(pull_rows_bulk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        pull_rows_bulk_kernel<__nv_bfloat16><<<grid_b, warps * 32, smem, s>>>(
+            bases, src_rank, src_row, scale, num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count,
+            static_cast<uint4*>(dst), cols / 8, wait_limit_cycles(), status);
+      } else {
+        MOE_CUDA(cudaFuncSetAttribute(pull_rows_bulk_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        pull_rows_bulk_kernel<__half><<<grid_b, warps * 32, smem, s>>>(
+            bases, src_rank, src_row, scale, num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count,
+            static_cast<uint4*>(dst), cols / 8, wait_limit_cycles(), status);
+      }
+      MOE_CUDA(cudaGetLastError());
+      return MOE_OK;
+    }
+    // rows too long for a slot: fall through to the load/store kernel
+  }
+  // The load/store kernel is bound by NVLink, not by SMs, and usually runs beside a grouped GEMM: a few CTAs per SM
+  // keep the links busy without taking issue slots from the GEMM.
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
+  const int grid = static_cast<int>(padded_rows < cap ? padded_rows : cap);
   if (dtype == MOE_DTYPE_BF16) {
     gather_rows_peer_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
                                                                        tile_pairs, num_experts, mtiles_bound,

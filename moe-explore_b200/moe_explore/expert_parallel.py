@@ -30,7 +30,6 @@ the CPU by itself.
 """
 from __future__ import annotations
 
-import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -38,7 +37,7 @@ import torch
 import torch.distributed as dist
 
 from moe_explore import _native
-from moe_explore.routing_plan import RoutingPlan, build_routing_plan
+from moe_explore.routing_plan import RoutingPlan, _report, build_routing_plan, device_status
 
 
 def _round_up(n: int, m: int) -> int:
@@ -73,6 +72,10 @@ def balanced_placement(expert_load, world: int) -> torch.Tensor:
 
 class NativeOps:
     """Row movement and local expert compute on the library's CUDA kernels."""
+
+    def status_word(self, device) -> torch.Tensor:
+        """The device status word the kernels report into (read together with the split sizes, once per step)."""
+        return device_status(device)
 
     def sort_by_expert(self, flat_experts: torch.Tensor, num_experts: int):
         """-> (perm int64 [R], counts int64 [E]) with the stable counting sort."""
@@ -166,8 +169,10 @@ def build_dispatch_layout(indices: torch.Tensor, num_experts: int, group, ops) -
     send_counts = counts.view(world, e_local).contiguous()
     recv_counts = torch.empty_like(send_counts)          # [source rank, local expert]
     dist.all_to_all_single(recv_counts, send_counts, group=group)
-    host = torch.stack((send_counts.sum(1), recv_counts.sum(1))).cpu()
-    send_splits, recv_splits = host[0].tolist(), host[1].tolist()
+    status = ops.status_word(flat.device).to(torch.int64) if hasattr(ops, "status_word") else torch.zeros(1, dtype=torch.int64, device=flat.device)
+    host = torch.cat((send_counts.sum(1), recv_counts.sum(1), status)).cpu()   # the one host read of the step
+    _report(int(host[-1]))                                                     # e.g. an expert id out of range
+    send_splits, recv_splits = host[:world].tolist(), host[world:2 * world].tolist()
     local_ids = torch.arange(e_local, device=flat.device).repeat(world)
     local_expert_ids = torch.repeat_interleave(local_ids, recv_counts.reshape(-1), output_size=sum(recv_splits))
     inv = torch.empty(R, dtype=torch.int32, device=flat.device)
@@ -246,7 +251,10 @@ class EPContext:
         # that shares an SM with a GEMM CTA gets almost none of the SM's L2 ingress (measured at 2 ranks: 37.8 ms
         # of pull kernels per step with every SM busy, 14.1 ms with 8 SMs free, the GEMMs no slower since they
         # are power-limited).  Nothing to gain with one rank: local rows arrive fast either way.
-        self.reserved_sms = int(os.environ.get("MOE_EP_RESERVED_SMS", "8")) if self.world > 1 else 0
+        self.reserved_sms = 8 if self.world > 1 else 0
+        # How rows are pulled: "bulk" = the copy-engine kernel (one CTA on each reserved SM, ~170 KB of remote reads
+        # in flight per SM), "ldst" = the load/store kernel spread over all SMs (64 KB in flight per SM).
+        self.pull_mode = "bulk"
         if allocate:
             self._allocate_symmetric()
 
@@ -297,7 +305,10 @@ def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: 
     dist.all_gather_into_tensor(gathered, counts.contiguous(), group=group)
     all_counts = gathered.view(world, num_experts)
     pair = all_counts.view(world, world, e_local).sum(-1)              # [source, owner] rows
-    host = pair.cpu()
+    status = ops.status_word(dev).to(torch.int64) if hasattr(ops, "status_word") else torch.zeros(1, dtype=torch.int64, device=dev)
+    host_all = torch.cat((pair.reshape(-1), status)).cpu()             # the one host read of the step
+    _report(int(host_all[-1]))                                         # e.g. an expert id out of range
+    host = host_all[:-1].view(world, world)
     send_splits, recv_splits = host[me].tolist(), host[:, me].tolist()
     num_received = sum(recv_splits)
     send_base = pair.cumsum(1) - pair                                   # start of each owner's segment at the source
@@ -376,22 +387,31 @@ class NativePeerOps(NativeOps):
         return [(c, n) for c in range(n)]
 
     @staticmethod
-    def _reserve_sms(ctx: EPContext):
-        """Cap the GEMM launches that follow so that ``ctx.reserved_sms`` SMs stay free for the pull kernels."""
-        if ctx.reserved_sms > 0:
-            sms = _native.query_device(ctx.device.index if ctx.device.index is not None else torch.cuda.current_device())[0]
-            _native.set_gemm_grid_limit(max(sms - ctx.reserved_sms, 2))
+    def _sm_count(ctx: EPContext) -> int:
+        return _native.query_device(ctx.device.index if ctx.device.index is not None else torch.cuda.current_device())[0]
+
+    @classmethod
+    def _gemm_options(cls, ctx: EPContext):
+        """Launch options that leave ``ctx.reserved_sms`` SMs free for the pull kernels (None: no cap)."""
+        if ctx.reserved_sms <= 0:
+            return None
+        return _native.gemm_options(max_ctas=max(cls._sm_count(ctx) - ctx.reserved_sms, 2))
 
     def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
         """Enqueue the pull of every chunk on the side stream; returns one event per chunk."""
         plan, chunks = lay.plan, self._chunks(ctx, lay)
         main = torch.cuda.current_stream()
         ctx.comm_stream.wait_stream(main)          # the layout arrays and the destination exist
+        # copy-engine pull: one CTA per reserved SM while GEMMs hold the others; every SM when nothing is reserved
+        bulk_ctas = 0
+        if ctx.pull_mode == "bulk":
+            bulk_ctas = ctx.reserved_sms if ctx.reserved_sms > 0 else self._sm_count(ctx)
         events = []
         with torch.cuda.stream(ctx.comm_stream):
             for chunk in chunks:
                 _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, scale, plan.num_mtiles, dst,
-                                         plan.tile_pairs, plan.num_experts, chunk)
+                                         plan.tile_pairs, plan.num_experts, chunk, bulk_ctas=bulk_ctas,
+                                         status=plan.status)
                 ev = torch.cuda.Event()
                 ev.record(ctx.comm_stream)
                 events.append(ev)
@@ -406,16 +426,15 @@ class NativePeerOps(NativeOps):
         xs, hidden, pre_act = new(rp, d), new(rp, weight2.size(1)), new(rp, weight1.size(2))
         main = torch.cuda.current_stream()
         events = self._pull_chunks(ctx, lay, None, xs)
-        self._reserve_sms(ctx)
+        capped = self._gemm_options(ctx)
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
             _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
-                                  False, act, plan.status, rows=lay.num_received / chunk[1], chunk=chunk)
+                                  False, act, plan.status, rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
             _native.mgrouped_gemm_push(hidden, weight2, ctx.y_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
                                        plan.tile_pairs, plan.num_mtiles, False, plan.status,
-                                       rows=lay.num_received / chunk[1], chunk=chunk)
-        _native.set_gemm_grid_limit(0)
+                                       rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
         return xs, hidden, pre_act
 
     def peer_backward(self, ctx: EPContext, lay: PeerLayout, state, weight1, weight2, act):
@@ -426,16 +445,16 @@ class NativePeerOps(NativeOps):
         gs, d_pre = new(rp, d), new(rp, pre_act.size(1))
         main = torch.cuda.current_stream()
         events = self._pull_chunks(ctx, lay, lay.p_scale, gs)      # score-scaled dOut rows
-        self._reserve_sms(ctx)
+        capped = self._gemm_options(ctx)
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
             _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
-                                       act, plan.status, rows=lay.num_received / chunk[1], chunk=chunk)
+                                       act, plan.status, rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
             _native.mgrouped_gemm_push(d_pre, weight1, ctx.dx_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
                                        plan.tile_pairs, plan.num_mtiles, True, plan.status,
-                                       rows=lay.num_received / chunk[1], chunk=chunk)
-        _native.set_gemm_grid_limit(0)                               # no pull runs beside the weight-gradient GEMMs
+                                       rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
+        # no pull runs beside the weight-gradient GEMMs: they use every SM
         d_w1 = torch.empty_like(weight1)
         _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status, rows=lay.num_received, tag="dw1")
         d_w2 = torch.empty_like(weight2)

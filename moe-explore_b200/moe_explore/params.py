@@ -47,6 +47,16 @@ class GLUInterleavedParams(FFNParams):
 
 
 @dataclass
+class SharedExpertParams(FFNParams):
+    """Shared expert(s) applied to every token: ``up_weight`` [S, d, I] (or [S, d, 2I] interleaved for *glu),
+    ``down_weight`` [S, I, d].  The reference reads exactly these three attributes
+    (functional/topk_moe.py:56-62) without declaring a type for them."""
+    up_weight: torch.Tensor
+    down_weight: torch.Tensor
+    activation: Activation
+
+
+@dataclass
 class RouterParams:
     """Base of the router parameter bundles."""
 

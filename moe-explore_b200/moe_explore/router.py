@@ -40,6 +40,48 @@ def topk_router(input: torch.Tensor, router_params: TopkRouterParams):
     return scores.to(input.dtype), indices
 
 
+class _FusedTopk(torch.autograd.Function):
+    """scores, indices = fused router tail of ``logits``; differentiable with respect to the logits."""
+
+    @staticmethod
+    def forward(ctx, logits, topk, softmax_before_topk, normalize_routing):
+        from moe_explore import _native
+
+        scores, indices, _ = _native.router_topk(logits, topk, softmax_before_topk, normalize_routing)
+        ctx.save_for_backward(logits, indices)
+        ctx.cfg = (softmax_before_topk, normalize_routing)
+        ctx.mark_non_differentiable(indices)
+        return scores, indices
+
+    @staticmethod
+    def backward(ctx, d_scores, _d_indices):
+        # the scores as a differentiable torch function of the logits GIVEN the selection (gather, not top-k)
+        logits, indices = ctx.saved_tensors
+        softmax_before_topk, normalize_routing = ctx.cfg
+        with torch.enable_grad():
+            leaf = logits.detach().requires_grad_(True)
+            if softmax_before_topk:
+                picked = torch.gather(softmax(leaf), -1, indices)
+            else:
+                picked = softmax(torch.gather(leaf, -1, indices))
+            if normalize_routing:
+                picked = picked / picked.sum(dim=-1, keepdim=True)
+            picked.to(logits.dtype).backward(d_scores)
+        return leaf.grad, None, None, None
+
+
+def fused_topk_router(input: torch.Tensor, router_params: TopkRouterParams):
+    """``topk_router`` with everything after the logits GEMM in ONE kernel (softmax, top-k, softmax over the k,
+    renormalisation, cast).  Opt-in: its tie rule is its own (equal logits are taken in ascending expert index; the
+    k results come in descending score order, where ``torch.topk(sorted=False)`` leaves the order unspecified), so
+    on inputs with tied logits among the selected values the indices can differ from ``topk_router``'s; without
+    such ties the set of experts per token is the same and the scores agree to one rounding of the 16-bit type.
+    (router.py:17-35)"""
+    logits = input @ router_params.router_weight
+    return _FusedTopk.apply(logits, router_params.topk, bool(router_params.softmax_before_topk),
+                            bool(router_params.normalize_routing))
+
+
 def ernie_router(input: torch.Tensor, router_params: ErnieRouterParams):
     """All-fp32 router with a selection-only bias and clamp-normalised weights (router.py:37-54)."""
     assert router_params.router_weight.dtype is torch.float32

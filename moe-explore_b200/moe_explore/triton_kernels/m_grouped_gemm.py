@@ -35,6 +35,10 @@ class MGroupedGEMMParams:
 
 
 def m_grouped_gemm(token: torch.Tensor, params: MGroupedGEMMParams, autotune_mode=None) -> torch.Tensor:
+    """Rows [g[e], g[e+1]) of the (optionally gathered) input times ``weight[e]``, optional activation epilogue,
+    optional scatter of the output rows.  As in the reference kernel the gather happens inside the GEMM's operand
+    loads and the scatter inside its epilogue (m_grouped_gemm.py:104-109, 168-172): no gathered copy of the input
+    and no un-scattered copy of the output exist."""
     assert token.dim() == 2
     assert params.weight.dim() == 3
     assert token.size(1) == params.weight.size(1)
@@ -45,6 +49,7 @@ def m_grouped_gemm(token: torch.Tensor, params: MGroupedGEMMParams, autotune_mod
     num_experts, k_dim, n_dim = params.weight.shape
     rows = params.num_tokens * params.topk if (params.gather or params.scatter) else params.num_tokens
     act = None if params.activation is None else str(params.activation)
+    assert act in _native.ACT_CODES, f"Invalid activation: {act}"
     out_cols = n_dim // 2 if is_glu(act) else n_dim
     out = torch.empty(rows, out_cols, dtype=token.dtype, device=token.device)
     if rows == 0:
@@ -52,22 +57,28 @@ def m_grouped_gemm(token: torch.Tensor, params: MGroupedGEMMParams, autotune_mod
 
     plan = plan_from_groups(params.group_indices.to(torch.int32), rows)
     token = token.contiguous()
-    a = torch.empty(plan.padded_rows, k_dim, dtype=token.dtype, device=token.device)
-    if params.gather:
-        # padded row p holds sorted position r = row_src[p]; its input row is token[perm[r] // topk]
+    weight = params.weight.contiguous()
+    # padded row p holds sorted position r = row_src[p]; with gather or scatter its flat (token, slot) position is
+    # perm[r]: the input row is token[perm[r] // topk], the output row perm[r]
+    flat_of_row = None
+    if params.gather or params.scatter:
         perm32 = params.permute_indices.to(torch.int32)
-        src = torch.where(plan.row_src >= 0, perm32[plan.row_src.clamp_min(0).long()], plan.row_src)
-        _native.gather_rows(token, src, plan.num_mtiles, a, params.topk)
-    else:
-        _native.gather_rows(token, plan.row_src, plan.num_mtiles, a, 1)
-
+        flat_of_row = torch.where(plan.row_src >= 0, perm32[plan.row_src.clamp_min(0).long()], plan.row_src)
+    in_rows = flat_of_row if params.gather else plan.row_src     # input row of padded row p (before // div)
+    in_div = params.topk if params.gather else 1
+    out_rows = flat_of_row if params.scatter else plan.row_src   # output row of padded row p
+    if not is_glu(act):
+        # element-wise epilogue: rows are gathered by the loads and scattered by the stores of the same kernel
+        _native.mgrouped_gemm_scatter(token, weight, out, out_rows, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
+                                      plan.padded_rows, False, act, a_row_src=in_rows, a_div=in_div, status=plan.status)
+        return out
+    # gated epilogue (two input columns per output column): output in the padded layout, then one un-pad pass
     y = torch.empty(plan.padded_rows, out_cols, dtype=token.dtype, device=token.device)
-    _native.mgrouped_gemm(a, params.weight.contiguous(), y, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act,
-                          plan.status)
+    _native.mgrouped_gemm_gather(token, in_rows, in_div, weight, y, None, plan.mtile_expert, plan.tile_pairs,
+                                 plan.num_mtiles, plan.padded_rows, act, plan.status)
     if params.scatter:
-        # out[perm[r]] = y[dst_row[r]]
         src_of_out = torch.empty(rows, dtype=torch.int32, device=token.device)
-        src_of_out[params.permute_indices] = plan.dst_row
+        src_of_out[params.permute_indices] = plan.dst_row   # out[perm[r]] = y[dst_row[r]]
         _native.unpad_rows(y, src_of_out, out)
     else:
         _native.unpad_rows(y, plan.dst_row, out)

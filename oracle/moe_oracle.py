@@ -155,7 +155,8 @@ def expert_compute(x: torch.Tensor, scores: torch.Tensor, indices: torch.Tensor,
                    weight2: torch.Tensor, act: str) -> torch.Tensor:
     """The per-expert loop of topk_moe_torch (topk_moe.py:80-102) with the in-place mul_ and
     scatter_reduce_ replaced by out-of-place multiply and index_add, so that autograd works.
-    x [T,d]; scores [T,k]; indices int64 [T,k]; weight1 [E,d,2I or I]; weight2 [E,I,d]."""
+    x [T,d]; scores [T,k]; indices int64 [T,k]; weight1 [E,d,2I or I]; weight2 [E,I,d] (in x's dtype, or a
+    narrower one that is upcast per expert: lets a checker hold 16-bit weights and compute in fp32)."""
     topk = indices.size(1)
     num_experts = weight1.size(0)
     found = get_token_indices(indices, topk, num_experts, zero_prefix=True)
@@ -168,8 +169,9 @@ def expert_compute(x: torch.Tensor, scores: torch.Tensor, indices: torch.Tensor,
             continue
         rows = found.indices[lo:hi]
         tok = rows // topk
-        h = activation(x[tok] @ weight1[e], act)
-        y = (h @ weight2[e]) * flat_scores[rows]
+        # weights stored in a narrower type than x are upcast one expert at a time (a no-op when the types agree)
+        h = activation(x[tok] @ weight1[e].to(x.dtype), act)
+        y = (h @ weight2[e].to(x.dtype)) * flat_scores[rows]
         out = out.index_add(0, tok, y)
     return out
 

@@ -18,8 +18,10 @@ def _declared_functions():
 
 def test_header_declares_the_expected_surface():
     names = _declared_functions()
-    for must in ("moe_routing_metadata", "moe_mgrouped_gemm", "moe_mgrouped_gemm_dglu", "moe_kgrouped_gemm",
-                 "moe_gather_rows", "moe_combine_topk", "moe_combine_bwd", "moe_last_error", "moe_query_device"):
+    for must in ("moe_routing_metadata", "moe_mgrouped_gemm", "moe_mgrouped_gemm_gather", "moe_mgrouped_gemm_combine",
+                 "moe_mgrouped_gemm_scatter", "moe_mgrouped_gemm_dglu", "moe_kgrouped_gemm", "moe_kgrouped_gemm_gather",
+                 "moe_gather_rows", "moe_combine_topk", "moe_combine_bwd", "moe_last_error", "moe_query_device",
+                 "moe_router_topk", "moe_set_wait_limit_cycles", "moe_read_status"):
         assert must in names
 
 
@@ -42,7 +44,7 @@ def test_size_helpers(native):
 
 def test_invalid_arguments_are_reported_not_launched(native):
     lib = native.load()
-    rc = lib.moe_mgrouped_gemm(None, None, None, None, None, None, None, 128, 64, 64, 1, 0, 0, 0, 0, 1, None, None)
+    rc = lib.moe_mgrouped_gemm(None, None, None, None, None, None, None, 128, 64, 64, 1, 0, 0, 0, 0, 1, None, None, None)
     assert rc == -1 and b"null" in lib.moe_last_error()
     rc = lib.moe_routing_metadata(None, -5, 8, None, None, None, None, None, None, None, None, None, None, 0, None)
     assert rc == -1 and b"negative" in lib.moe_last_error()
@@ -52,16 +54,28 @@ def test_invalid_arguments_are_reported_not_launched(native):
     p = ctypes.addressof(buf)
     p += (-p) % 16  # the library checks 16-byte alignment before anything else
     # K not a multiple of 8 (the reference's K=300, N=20 test shape): unsupported, stated clearly
-    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 300, 20, 2, 0, 0, 0, 0, 1, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 300, 20, 2, 0, 0, 0, 0, 1, None, None, None)
     assert rc == -2 and b"multiples of 8" in lib.moe_last_error()
-    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 100, 64, 64, 2, 0, 0, 0, 0, 1, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 100, 64, 64, 2, 0, 0, 0, 0, 1, None, None, None)
     assert rc == -1 and b"padded_rows" in lib.moe_last_error()
-    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 64, 64, 2, 0, 9, 0, 0, 1, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 64, 64, 2, 0, 9, 0, 0, 1, None, None, None)
     assert rc == -1 and b"activation" in lib.moe_last_error()
-    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, None, p, 128, 64, 64, 2, 0, 0, 0, 1, 4, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, None, p, 128, 64, 64, 2, 0, 0, 0, 1, 4, None, None, None)
     assert rc == -1 and b"chunk" in lib.moe_last_error()   # chunked launches need the tile-pair list
-    rc = lib.moe_kgrouped_gemm(p, p, p, p, 128, 64, 60, 2, 0, None, None)
+    rc = lib.moe_mgrouped_gemm(p, p, p, None, p, p, p, 128, 64, 64, 2, 1, 3, 0, 0, 1, None, None, None)
+    assert rc == -1 and b"gated" in lib.moe_last_error()   # a gated epilogue reads w as [E, K, N] only
+    rc = lib.moe_mgrouped_gemm_gather(p, 0, p, 2, p, p, None, p, p, p, 128, 64, 64, 2, 0, 0, None, None, None)
+    assert rc == -1 and b"gathered" in lib.moe_last_error()   # the gathered tensor needs at least one row
+    rc = lib.moe_mgrouped_gemm_scatter(p, 128, None, 1, p, p, p, p, p, p, 128, 64, 64, 2, 0, 3, 0, None, None, None)
+    assert rc == -1 and b"element-wise" in lib.moe_last_error()
+    rc = lib.moe_mgrouped_gemm_combine(p, p, p, None, None, 2, p, p, p, 128, 64, 64, 2, 0, 0, None, None, None)
+    assert rc == -1 and b"null" in lib.moe_last_error()
+    rc = lib.moe_kgrouped_gemm(p, p, p, p, 128, 64, 60, 2, 0, None, None, None)
     assert rc == -2
+    rc = lib.moe_router_topk(p, p, p, None, 4, 2000, 2, 0, 0, 0, None)
+    assert rc == -2 and b"E <=" in lib.moe_last_error()
+    rc = lib.moe_router_topk(p, p, p, None, 4, 8, 2, 0, 0, 7, None)
+    assert rc == -1 and b"dtype" in lib.moe_last_error()
     rc = lib.moe_combine_topk(p, None, p, p, 4, 0, 64, 0, None)
     assert rc == -1
     rc = lib.moe_gather_rows(p, 4, p, p, p, 128, 64, 1, 7, None)

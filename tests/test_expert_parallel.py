@@ -217,8 +217,9 @@ def test_balanced_placement_is_a_permutation_and_evens_the_load():
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("pull_mode", ["bulk", "ldst"])   # copy-engine pull kernel / load-store pull kernel
 @pytest.mark.parametrize("E", [16, 32, 80])   # 32 and more local experts: the geometric pipeline schedule
-def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, native):
+def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, pull_mode, native):
     from moe_explore.expert_compute import expert_compute
     from moe_explore.expert_parallel import ep_expert_compute
     from moe_explore.routing_plan import build_routing_plan
@@ -236,6 +237,7 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, native):
         from moe_explore.expert_parallel import EPContext
 
         context = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, torch.device("cuda", 0))
+        context.pull_mode = pull_mode
         outs = []
         for mode in ("peer", "collective", "single"):
             leaves = [t.detach().clone().requires_grad_() for t in (x, scores, w1, w2)]
@@ -248,6 +250,9 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, native):
             out.backward(grad)
             outs.append([out.detach()] + [t.grad for t in leaves])
         torch.cuda.synchronize()
+        from moe_explore.routing_plan import check_device_status
+
+        assert check_device_status() == 0
         # same kernels on the same rows in the same expert order: forward, dx, dscores identical; weight
         # gradients too (row order inside an expert is the stable order in both paths)
         for other in outs[:2]:

@@ -195,8 +195,8 @@ def test_chunked_launches_cover_every_tile_exactly_once(chunks, native):
 
 @pytest.mark.parametrize("limit", [2, 36, 140])
 def test_capped_grid_gives_the_same_result(limit, native):
-    """moe_set_gemm_grid_limit only changes how many persistent CTAs share the tiles (also for the long contraction
-    that uses the grid-wide wave counter, K >= 8192): outputs are bit-identical to the uncapped launch."""
+    """``max_ctas`` of the launch options only changes how many persistent CTAs share the tiles (also for the long
+    contraction that uses the grid-wide wave counter, K >= 8192): outputs are bit-identical to the uncapped launch."""
     from moe_explore.routing_plan import build_routing_plan
 
     g = torch.Generator().manual_seed(limit)
@@ -208,21 +208,179 @@ def test_capped_grid_gives_the_same_result(limit, native):
     wt = (torch.randn(E, N, K, generator=g) * 0.02).to(torch.bfloat16).cuda()
     n = int(plan.num_mtiles[0].item()) * 128
 
-    def run():
+    def run(options):
         out = torch.zeros(plan.padded_rows, N, dtype=torch.bfloat16, device="cuda")
         out_t = torch.zeros_like(out)
-        native.mgrouped_gemm(a, w, out, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status)
-        native.mgrouped_gemm(a, wt, out_t, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, True, None, plan.status)
+        native.mgrouped_gemm(a, w, out, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status,
+                             options=options)
+        native.mgrouped_gemm(a, wt, out_t, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, True, None, plan.status,
+                             options=options)
         dw = torch.empty(E, K // 16, N, dtype=torch.bfloat16, device="cuda")
-        native.kgrouped_gemm(a[:, : K // 16].contiguous(), out, dw, plan.pad_offsets, plan.status)
+        native.kgrouped_gemm(a[:, : K // 16].contiguous(), out, dw, plan.pad_offsets, plan.status, options=options)
         plan.check()
         return out[:n].clone(), out_t[:n].clone(), dw
 
-    whole = run()
-    native.set_gemm_grid_limit(limit)
-    try:
-        capped = run()
-    finally:
-        native.set_gemm_grid_limit(0)
+    whole = run(None)
+    capped = run(native.gemm_options(max_ctas=limit))
     for x, y in zip(whole, capped):
         assert torch.equal(x, y)
+
+
+def _small_problem(native, seed, E=6, T=1500, K=256, N=512, k=1):
+    from moe_explore.routing_plan import build_routing_plan
+
+    g = torch.Generator().manual_seed(seed)
+    idx = torch.randint(0, E, (T, k), generator=g)
+    plan = build_routing_plan(idx.cuda(), E, k)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(E, K, N, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    return plan, x, w, g
+
+
+@pytest.mark.parametrize("act", [None, "swiglu", "silu"])
+@pytest.mark.parametrize("k", [1, 4])
+@pytest.mark.parametrize("single_cta", [0, 1])
+def test_rows_gathered_by_the_operand_loads_equal_rows_copied_first(act, k, single_cta, native):
+    """moe_mgrouped_gemm_gather (tile::gather4 loads of the token rows) against the dispatch copy followed by the
+    plain GEMM: the same tiles meet the same tensor-core instructions, so the outputs are bit-identical."""
+    plan, x, w, _ = _small_problem(native, 3 + k, k=k, T=777)
+    rp = plan.padded_rows
+    n = int(plan.num_mtiles[0].item()) * 128
+    cols = w.size(2) // 2 if act == "swiglu" else w.size(2)
+    opts = native.gemm_options(single_cta=single_cta)
+    xs = torch.empty(rp, x.size(1), dtype=x.dtype, device="cuda")
+    native.dispatch_rows(x, plan.dst_row, plan.row_src, plan.num_mtiles, xs, k)
+    ref, ref_pre = torch.zeros(rp, cols, dtype=x.dtype, device="cuda"), torch.zeros(rp, w.size(2), dtype=x.dtype, device="cuda")
+    native.mgrouped_gemm(xs, w, ref, ref_pre if act else None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act,
+                         plan.status, options=opts)
+    out, pre = torch.zeros_like(ref), torch.zeros_like(ref_pre)
+    native.mgrouped_gemm_gather(x, plan.row_src, k, w, out, pre if act else None, plan.mtile_expert, plan.tile_pairs,
+                                plan.num_mtiles, rp, act, plan.status, options=opts)
+    plan.check()
+    assert torch.equal(out[:n], ref[:n])
+    if act:
+        assert torch.equal(pre[:n], ref_pre[:n])
+    # the weight-gradient contraction with its first operand gathered the same way
+    b = torch.randn(rp, 256, device="cuda").to(torch.bfloat16) * (plan.row_src >= 0)[:, None]
+    dw_ref = torch.empty(w.size(0), x.size(1), 256, dtype=x.dtype, device="cuda")
+    dw = torch.empty_like(dw_ref)
+    native.kgrouped_gemm(xs, b, dw_ref, plan.pad_offsets, plan.status, options=opts)
+    native.kgrouped_gemm_gather(x, plan.row_src, k, b, dw, plan.pad_offsets, plan.status, options=opts)
+    plan.check()
+    assert torch.equal(dw, dw_ref)
+
+
+@pytest.mark.parametrize("k,N", [(2, 512), (8, 320)])
+def test_fold_fused_into_the_epilogue_against_the_separate_fold(k, N, native):
+    """moe_mgrouped_gemm_combine (router weight x row, added into token order by vector reductions) against the
+    grouped GEMM + deterministic fold: equal up to the extra 16-bit roundings of the k-1 partial sums."""
+    plan, x, w, g = _small_problem(native, 9 + k, k=k, T=640, N=N)
+    T = 640
+    rp = plan.padded_rows
+    xs = torch.empty(rp, x.size(1), dtype=x.dtype, device="cuda")
+    native.dispatch_rows(x, plan.dst_row, plan.row_src, plan.num_mtiles, xs, k)
+    scores = torch.softmax(torch.randn(T, k, generator=g), -1).to(torch.bfloat16).cuda()
+    ys = torch.empty(rp, N, dtype=x.dtype, device="cuda")
+    native.mgrouped_gemm(xs, w, ys, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status)
+    ref = torch.empty(T, N, dtype=x.dtype, device="cuda")
+    native.combine_topk(ys, scores, plan.dst_row, ref, k)
+    out = torch.zeros(T, N, dtype=x.dtype, device="cuda")
+    native.mgrouped_gemm_combine(xs, w, out, plan.row_src, scores, k, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
+                                 False, plan.status)
+    plan.check()
+    assert relerr(out, ref) <= 2e-2 and out.isfinite().all()
+    # unweighted (scores = None)
+    ref1 = torch.empty_like(ref)
+    native.combine_topk(ys, None, plan.dst_row, ref1, k)
+    out1 = torch.zeros_like(out)
+    native.mgrouped_gemm_combine(xs, w, out1, plan.row_src, None, k, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
+                                 False, plan.status)
+    assert relerr(out1, ref1) <= 2e-2
+
+
+@pytest.mark.parametrize("act", ["approx_gelu", "gelu", "silu", None])
+def test_elementwise_activations_of_the_generic_wrapper(act, native):
+    """The activation strings the reference's wrapper accepts (triton_kernels/activation.py:38-45), ``approx_gelu``
+    (tanh form) among them, with gather and with scatter."""
+    from moe_explore.expert_permute import get_token_indices
+    from moe_explore.triton_kernels.m_grouped_gemm import MGroupedGEMMParams, m_grouped_gemm
+
+    T, E, k, K, N = 300, 8, 2, 256, 384
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(E, K, N, generator=g) / math.sqrt(N)).to(torch.bfloat16)
+    _, idx = _routing(T, E, k, g)
+    found = get_token_indices(idx.cuda(), k, E, zero_prefix=True)
+    tfn = {"approx_gelu": lambda v: torch.nn.functional.gelu(v, approximate="tanh"), "gelu": torch.nn.functional.gelu,
+           "silu": torch.nn.functional.silu, None: lambda v: v}[act]
+    out = m_grouped_gemm(x.cuda(), MGroupedGEMMParams(w.cuda(), found.group_indices, found.indices, True, False, T, k,
+                                                      activation=act))
+    ref = tfn(O.grouped_matmul(x.float(), w.float(), found.group_indices.cpu(), found.indices.cpu(), gather=True, topk=k))
+    assert relerr(out.cpu(), ref) <= TOL
+    xr = torch.randn(T * k, K, generator=g).to(torch.bfloat16)
+    out = m_grouped_gemm(xr.cuda(), MGroupedGEMMParams(w.cuda(), found.group_indices, found.indices, False, True, T, k,
+                                                       activation=act))
+    ref = tfn(O.grouped_matmul(xr.float(), w.float(), found.group_indices.cpu(), found.indices.cpu(), scatter=True))
+    assert relerr(out.cpu(), ref) <= TOL
+    with pytest.raises(AssertionError):
+        m_grouped_gemm(x.cuda(), MGroupedGEMMParams(w.cuda(), found.group_indices, found.indices, True, False, T, k,
+                                                    activation="relu"))
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_stays_usable(native):
+    """The wave barrier of a long contraction is told to wait for one worker more than the launch has (a flag that
+    nothing sets), with a short wait limit: the kernel returns by itself, the status word holds the time-out code,
+    the launch's own result is still right (the barrier is only an optimisation: its workers carry on unsynchronised),
+    and the next ordinary launch is right as well."""
+    import warnings
+
+    from moe_explore.routing_plan import build_routing_plan
+
+    g = torch.Generator().manual_seed(77)
+    E, T, K, N = 4, 6000, 8192, 1024      # ~24 row-tile pairs x 4 column tiles: more work items than workers
+    idx = torch.randint(0, E, (T, 1), generator=g)
+    plan = build_routing_plan(idx.cuda(), E, 1)
+    a = torch.randn(plan.padded_rows, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(E, K, N, generator=g) * 0.02).to(torch.bfloat16).cuda()
+    n = int(plan.num_mtiles[0].item()) * 128
+    ref = torch.zeros(plan.padded_rows, N, dtype=torch.bfloat16, device="cuda")
+    native.mgrouped_gemm(a, w, ref, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status,
+                         options=native.gemm_options(wave_sync=-1))
+    plan.check()
+    sms = native.query_device(0)[0]
+    native.set_wait_limit_cycles(2_000_000)   # ~1 ms for every wait, a quarter of it for the wave barrier
+    try:
+        out = torch.zeros_like(ref)
+        native.mgrouped_gemm(a, w, out, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status,
+                             options=native.gemm_options(wave_sync=1, wave_workers=sms))   # more than sms / 2 pairs exist
+        torch.cuda.synchronize()
+    finally:
+        native.set_wait_limit_cycles(0)
+    assert native.read_status(plan.status) == native.STATUS_WAVE_FALLBACK
+    with pytest.raises(native.MoeNativeError, match="wave barrier"):
+        native.check_status(plan.status)
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        plan.check()                           # the Python layer treats it as a warning and clears the word
+    assert any("wave barrier" in str(m.message) for m in seen)
+    assert torch.equal(out[:n], ref[:n])
+    again = torch.zeros_like(ref)
+    native.mgrouped_gemm(a, w, again, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status)
+    plan.check()
+    assert torch.equal(again[:n], ref[:n])
+
+
+def test_metadata_built_for_another_row_bound_is_refused(native):
+    """padded_rows must be the bound the metadata was built with: a caller that passes fewer rows is told so through
+    the status word and nothing is computed from misread scheduling words."""
+    plan, x, w, _ = _small_problem(native, 21)
+    rp = plan.padded_rows
+    xs = torch.zeros(rp, x.size(1), dtype=x.dtype, device="cuda")
+    out = torch.full((rp - 128, w.size(2)), 3.0, dtype=x.dtype, device="cuda")
+    native.mgrouped_gemm(xs[: rp - 128], w, out, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None,
+                         plan.status)
+    torch.cuda.synchronize()
+    assert int(plan.status.item()) == native.STATUS_BAD_LAYOUT
+    assert bool((out == 3.0).all())
+    with pytest.raises(native.MoeNativeError, match="does not describe"):
+        plan.check()

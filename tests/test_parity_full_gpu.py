@@ -1,0 +1,191 @@
+"""Forward AND backward of the CUDA path against the fp32 oracle at the benchmark configurations' full sizes.
+
+Every case runs ``expert_compute`` (routing metadata -> grouped GEMMs -> fold, and its backward) on seeded bf16
+inputs of the configuration's shape and compares out, dX, dScores, dW1 and dW2 with ``oracle.moe_oracle`` run in fp32
+ON THE GPU from the same bf16-rounded inputs and the same routing decision (the oracle is device-agnostic torch; the
+weights are upcast per block of experts so that the fp32 copies and their gradients stay small).  Per tensor:
+
+  * max |a - b| / max |b| <= 2e-2                        (the stated bf16 tolerance)
+  * element-wise pass rate under the reference's own rule (src/moe_explore/testing.py:340-357: atol and rtol
+    derived from the dtype's epsilon, the row length and the largest value) >= 0.99
+  * cosine similarity >= 0.999
+  * experts that received no row have exactly zero weight gradients.
+
+Configurations: Mixtral-8x7B (T=8192, d=4096, E=8, top-2, I=14336, linear router), Qwen1.5-MoE (T=16384, d=2048,
+E=60, top-4, I=1408, logits + per-expert bias), the OLMoE-shaped stress layer (d=2048, E=64, top-8, I=1024) at
+T=8192 for the three router distributions and at T=65536 for the degenerate one, and the DeepSeek-V3 shape
+(d=7168, E=256, top-8, I=2048, Zipf(1.1) popularity) at T=4096 tokens.  Synthetic seeded inputs stand in for model
+activations and checkpoints.  The measured figures are also written to gpurun_out/parity_full.json when that folder
+exists.
+"""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from conftest import ROOT
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL = 2e-2
+RESULTS = {}
+
+
+def metrics(a, b, k=None):
+    """``k``: the length the reference's rule scales its tolerances with (its a.size(-1); the contraction length for
+    the router-weight gradient, whose rows are only top-k long)."""
+    a, b = a.float(), b.float()
+    diff = (a - b).abs()
+    max_rel = float(diff.max() / b.abs().max().clamp_min(1e-30))
+    eps = 0.0078125            # bf16, as in the reference's rule
+    k = a.size(-1) if k is None else k
+    m = float(torch.maximum(a.max(), b.max()))
+    atol = min(1e-2, k * m * eps * 1e-2)
+    rtol = math.sqrt(k) * eps * 1e-1
+    passed = float((diff <= atol + rtol * b.abs()).float().mean())
+    cos = float(torch.nn.functional.cosine_similarity(a.reshape(1, -1).double(), b.reshape(1, -1).double()).item())
+    return dict(max_rel=max_rel, pass_rate=passed, cosine=cos)
+
+
+def merge(worst, new):
+    if worst is None:
+        return dict(new)
+    return dict(max_rel=max(worst["max_rel"], new["max_rel"]), pass_rate=min(worst["pass_rate"], new["pass_rate"]),
+                cosine=min(worst["cosine"], new["cosine"]))
+
+
+def make_logits(router, T, E, gen, x=None):
+    dev = "cuda"
+    if router == "logits":
+        return torch.randn(T, E, generator=gen, device=dev)
+    if router == "logits_bias":
+        return torch.randn(T, E, generator=gen, device=dev) + torch.randn(E, generator=gen, device=dev) * 0.5
+    if router == "degenerate":
+        logits = torch.randn(T, E, generator=gen, device=dev)
+        hot = torch.rand(T, generator=gen, device=dev) < 0.95
+        logits[hot, 5] += 20.0
+        logits[:, E - 8:] = -1e4
+        return logits
+    if router.startswith("zipf"):
+        s = float(router[4:]) / 10.0
+        p = torch.arange(1, E + 1, dtype=torch.float32, device=dev) ** (-s)
+        p = (p / p.sum())[torch.randperm(E, generator=gen, device=dev)]
+        u = torch.rand(T, E, generator=gen, device=dev).clamp_min(1e-20)
+        return torch.log(p) - torch.log(-torch.log(u))
+    if router == "linear":
+        wr = (torch.randn(x.size(1), E, generator=gen, device=dev) * 0.02).bfloat16()
+        return (x @ wr).float()
+    raise ValueError(router)
+
+
+def make_case(T, d, E, k, I, router, seed):
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+    x = torch.randn(T, d, generator=gen, device="cuda").bfloat16()
+    grad = torch.randn(T, d, generator=gen, device="cuda").bfloat16()
+    w1 = torch.empty(E, d, 2 * I, dtype=torch.bfloat16, device="cuda")
+    w2 = torch.empty(E, I, d, dtype=torch.bfloat16, device="cuda")
+    for e in range(E):
+        w1[e] = (torch.randn(d, 2 * I, generator=gen, device="cuda") * 0.02).bfloat16()
+        w2[e] = (torch.randn(I, d, generator=gen, device="cuda") * 0.02).bfloat16()
+    logits = make_logits(router, T, E, gen, x)
+    top, idx = torch.topk(logits, k, dim=-1, sorted=False)
+    scores = torch.softmax(top, dim=-1, dtype=torch.float32).bfloat16()
+    return x, grad, w1, w2, scores, idx
+
+
+def run_ours(x, grad, w1, w2, scores, idx, gather_in_gemm):
+    from moe_explore.expert_compute import expert_compute
+    from moe_explore.routing_plan import build_routing_plan, check_device_status
+
+    leaves = [t.detach().requires_grad_() for t in (x, scores, w1, w2)]
+    plan = build_routing_plan(idx, w1.size(0), idx.size(1), want_perm=False)
+    out = expert_compute(*leaves, plan, "swiglu", gather_in_gemm=gather_in_gemm)
+    out.backward(grad)
+    assert check_device_status() == 0
+    counts = (plan.group_indices[1:] - plan.group_indices[:-1]).cpu()
+    return out.detach(), [t.grad for t in leaves], counts
+
+
+def compare_with_oracle(name, x, grad, w1, w2, scores, idx, ours, block):
+    """The oracle over blocks of ``block`` experts: a block sees every (token, slot) pair, the pairs of other blocks
+    with weight zero on one of its own experts -- they add exactly nothing to its output and weight gradients -- so the
+    sum over blocks is the layer, and only one block's fp32 weights and gradients exist at a time."""
+    out, (dx, dscores, dw1, dw2), counts = ours
+    E = w1.size(0)
+    xf, gf, sf = x.float(), grad.float(), scores.float()
+    ref_out = torch.zeros_like(xf)
+    ref_dx = torch.zeros_like(xf)
+    ref_ds = torch.zeros_like(sf)
+    res = {}
+    for b0 in range(0, E, block):
+        b1 = min(b0 + block, E)
+        inside = (idx >= b0) & (idx < b1)
+        idx_b = torch.where(inside, idx - b0, idx % (b1 - b0))
+        s_b = torch.where(inside, sf, torch.zeros_like(sf)).requires_grad_()
+        x_b = xf.detach().clone().requires_grad_()
+        w1_b = w1[b0:b1].float().requires_grad_()
+        w2_b = w2[b0:b1].float().requires_grad_()
+        o = O.expert_compute(x_b, s_b, idx_b, w1_b, w2_b, "swiglu")
+        o.backward(gf)
+        ref_out += o.detach()
+        ref_dx += x_b.grad
+        ref_ds += torch.where(inside, s_b.grad, torch.zeros_like(sf))
+        res["dw1"] = merge(res.get("dw1"), metrics(dw1[b0:b1], w1_b.grad))
+        res["dw2"] = merge(res.get("dw2"), metrics(dw2[b0:b1], w2_b.grad))
+        del o, x_b, s_b, w1_b, w2_b
+    res["out"] = metrics(out, ref_out)
+    res["dx"] = metrics(dx, ref_dx)
+    res["dscores"] = metrics(dscores, ref_ds, k=x.size(1))
+    empty = (counts == 0).nonzero().flatten().tolist()
+    for e in empty:
+        assert int(dw1[e].abs().sum()) == 0 and int(dw2[e].abs().sum()) == 0, f"expert {e} has no rows"
+    RESULTS[name] = dict(res, empty_experts=len(empty))
+    out_dir = os.path.join(ROOT, "gpurun_out")
+    if os.path.isdir(out_dir):
+        with open(os.path.join(out_dir, "parity_full.json"), "w") as f:
+            json.dump(RESULTS, f, indent=1)
+    for tensor, m in res.items():
+        assert m["max_rel"] <= TOL, f"{name} {tensor}: max relative error {m['max_rel']:.3e}"
+        assert m["pass_rate"] >= 0.99, f"{name} {tensor}: element-wise pass rate {m['pass_rate']:.5f}"
+        assert m["cosine"] >= 0.999, f"{name} {tensor}: cosine {m['cosine']:.6f}"
+    return res
+
+
+def run_case(name, T, d, E, k, I, router, seed, block=None, gather_in_gemm=None):
+    torch.cuda.empty_cache()
+    case = make_case(T, d, E, k, I, router, seed)
+    ours = run_ours(*case, gather_in_gemm)
+    res = compare_with_oracle(name, *case, ours, block or E)
+    del case, ours
+    torch.cuda.empty_cache()
+    return res
+
+
+def test_mixtral_8x7b_full_size(native):
+    run_case("mixtral_8x7b", 8192, 4096, 8, 2, 14336, "linear", seed=0, block=4)
+
+
+@pytest.mark.parametrize("gather_in_gemm", [True, False])
+def test_qwen15_moe_full_size(gather_in_gemm, native):
+    run_case(f"qwen15_moe_a27b[gather_in_gemm={gather_in_gemm}]", 16384, 2048, 60, 4, 1408, "logits_bias", seed=1,
+             gather_in_gemm=gather_in_gemm)
+
+
+@pytest.mark.parametrize("router", ["logits", "zipf15", "degenerate"])
+def test_olmoe_stress_layer_8192_tokens(router, native):
+    res = run_case(f"olmoe_8192[{router}]", 8192, 2048, 64, 8, 1024, router, seed=2)
+    if router == "degenerate":
+        assert RESULTS[f"olmoe_8192[{router}]"]["empty_experts"] >= 8
+    assert res["out"]["max_rel"] <= TOL
+
+
+def test_olmoe_stress_layer_65536_tokens_degenerate(native):
+    run_case("olmoe_65536[degenerate]", 65536, 2048, 64, 8, 1024, "degenerate", seed=3)
+    assert RESULTS["olmoe_65536[degenerate]"]["empty_experts"] >= 8
+
+
+def test_deepseek_v3_shape_4096_tokens(native):
+    run_case("deepseek_v3[T=4096]", 4096, 7168, 256, 8, 2048, "zipf11", seed=4, block=64)

@@ -24,7 +24,8 @@ def _check_against_oracle(idx, E):
     assert torch.equal(plan.group_indices.cpu(), ref.group_indices)
     assert plan.perm.dtype == torch.int64 and torch.equal(plan.perm.cpu(), ref.indices)
     po, row_src, dst_row, mte = O.padded_layout(idx.cpu(), E)
-    n, num_pairs = plan.num_mtiles.tolist()
+    n, num_pairs, bound_written, _ = plan.num_mtiles.tolist()
+    assert bound_written == plan.mtile_expert.numel()
     assert n == int(po[-1]) // 128
     # tile pairs: every tile appears exactly once, both tiles of a pair belong to the same expert
     pairs = plan.tile_pairs[:num_pairs].cpu().tolist()
@@ -122,11 +123,80 @@ def test_out_of_range_ids_are_flagged_not_placed(native):
     plan = _plan(idx, 4, 2)
     assert plan.group_indices.cpu().tolist() == [0, 1, 2, 3, 4]
     assert int(plan.status.item()) == 100
+    # dropped positions are marked, not left undefined: no padded row, and the tail of the permutation is -1
+    assert plan.dst_row.cpu().tolist()[2] == -1 and plan.dst_row.cpu().tolist()[5] == -1
+    assert plan.perm.cpu().tolist()[4:] == [-1, -1] and sorted(plan.perm.cpu().tolist()[:4]) == [0, 1, 3, 4]
     with pytest.raises(MoeNativeError, match="outside"):
         plan.check()
+    assert int(plan.status.item()) == 0   # reading the word clears it
+
+
+def test_layer_with_an_out_of_range_id_stays_in_bounds(native):
+    """One bad expert id in a whole forward + backward: the status word says so, the (token, slot) pairs with the bad
+    id contribute nothing, every other output equals the layer run on the valid pairs alone, and every index a kernel
+    consumed was either a valid row or the -1 marker (checked on the host)."""
+    from moe_explore._native import MoeNativeError
+    from moe_explore.expert_compute import expert_compute
+    from moe_explore.routing_plan import build_routing_plan
+
+    T, d, E, k, I = 300, 128, 8, 2, 256
+    g = torch.Generator(device="cuda").manual_seed(5)
+    mk = lambda *s, std=1.0: (torch.randn(*s, generator=g, device="cuda") * std).bfloat16()
+    x, w1, w2, grad = mk(T, d), mk(E, d, 2 * I, std=0.05), mk(E, I, d, std=0.05), mk(T, d)
+    idx = torch.topk(torch.randn(T, E, generator=g, device="cuda"), k, dim=-1, sorted=False).indices
+    scores = torch.softmax(torch.randn(T, k, generator=g, device="cuda"), -1).bfloat16()
+    bad = idx.clone()
+    bad[17, 1] = E + 3          # out of range
+    bad[101, 0] = -2            # negative
+    for gather_in_gemm in (False, True):
+        leaves = [t.detach().clone().requires_grad_() for t in (x, scores, w1, w2)]
+        plan = build_routing_plan(bad, E, k)
+        out = expert_compute(*leaves, plan, "swiglu", gather_in_gemm=gather_in_gemm)
+        out.backward(grad)
+        torch.cuda.synchronize()
+        assert int(plan.status.item()) == 100
+        rp = plan.padded_rows
+        dst, src, perm = plan.dst_row.cpu(), plan.row_src.cpu(), plan.perm.cpu()
+        assert ((dst == -1) | ((dst >= 0) & (dst < rp))).all() and int((dst == -1).sum()) == 2
+        assert ((src == -1) | ((src >= 0) & (src < T * k)))[: int(plan.num_mtiles[0]) * 128].all()
+        assert ((perm == -1) | ((perm >= 0) & (perm < T * k))).all() and int((perm == -1).sum()) == 2
+        with pytest.raises(MoeNativeError, match="outside"):
+            plan.check()
+        # reference: the same layer with the two bad slots given weight zero and any valid expert
+        ok_idx = bad.clone()
+        ok_idx[17, 1] = 0
+        ok_idx[101, 0] = 0
+        ok_scores = scores.float().clone()
+        ok_scores[17, 1] = 0
+        ok_scores[101, 0] = 0
+        ref = O.layer_fwd_bwd(x.float(), ok_scores, ok_idx, w1.float(), w2.float(), "swiglu", grad.float())
+        rel = lambda a, b: float((a.float() - b.float()).abs().max() / b.float().abs().max())
+        assert out.isfinite().all() and rel(out, ref[0]) <= 2e-2
+        assert rel(leaves[0].grad, ref[1]) <= 2e-2 and rel(leaves[2].grad, ref[3]) <= 2e-2 and rel(leaves[3].grad, ref[4]) <= 2e-2
+        ds = leaves[1].grad.float()
+        assert float(ds[17, 1]) == 0.0 and float(ds[101, 0]) == 0.0
+        mask = torch.ones(T, k, dtype=torch.bool, device="cuda")
+        mask[17, 1] = mask[101, 0] = False
+        assert rel(ds[mask], ref[2][mask]) <= 2e-2
+
+
+def test_group_prefix_that_is_not_a_prefix_is_reported(native):
+    """plan_from_groups with a prefix that does not end at the row count (or is not monotone): status 5, the
+    offending rows get no padded row, nothing is written out of bounds."""
+    from moe_explore._native import MoeNativeError
+    from moe_explore.routing_plan import plan_from_groups
+
+    for groups in ([0, 40, 100, 90], [0, 40, 100, 130], [5, 40, 100, 128]):
+        plan = plan_from_groups(torch.tensor(groups, dtype=torch.int32, device="cuda"), 128)
+        torch.cuda.synchronize()
+        assert int(plan.status.item()) == 5
+        dst = plan.dst_row.cpu()
+        assert ((dst == -1) | ((dst >= 0) & (dst < plan.padded_rows))).all()
+        with pytest.raises(MoeNativeError, match="does not describe"):
+            plan.check()
 
 
 def test_empty_input(native):
     plan = _plan(torch.zeros(0, 2, dtype=torch.int64), 8, 2)
     assert plan.group_indices.cpu().tolist() == [0] * 9
-    assert plan.num_mtiles.tolist() == [0, 0]
+    assert plan.num_mtiles.tolist()[:2] == [0, 0]

@@ -24,7 +24,7 @@ def _outputs(num_rows, num_experts, native):
                 perm=torch.full((num_rows,), -3, dtype=torch.int64, device="cuda"),
                 pad_offsets=torch.full((num_experts + 1,), -3, **i32), row_src=torch.full((rp,), -3, **i32),
                 dst_row=torch.full((num_rows,), -3, **i32), mtile_expert=torch.full((rp // 128,), -3, **i32),
-                tile_pairs=torch.full((rp // 128 + num_experts + 1,), -3, **i32), num_mtiles=torch.full((2,), -3, **i32),
+                tile_pairs=torch.full((rp // 128 + num_experts + 1,), -3, **i32), num_mtiles=torch.full((4,), -3, **i32),
                 status=torch.zeros(1, **i32))
 
 
@@ -38,8 +38,8 @@ def _run_both(idx, num_experts, native):
     native.routing_metadata_static(flat, num_experts, b["group_indices"], b["perm"], b["pad_offsets"], b["row_src"],
                                    b["dst_row"], b["mtile_expert"], b["tile_pairs"], b["num_mtiles"], b["status"])
     torch.cuda.synchronize()
-    n, pairs = a["num_mtiles"].tolist()
-    assert [n, pairs] == b["num_mtiles"].tolist()
+    n, pairs = a["num_mtiles"].tolist()[:2]
+    assert a["num_mtiles"].tolist() == b["num_mtiles"].tolist()
     assert torch.equal(a["tile_pairs"][:pairs], b["tile_pairs"][:pairs])
     bound = a["mtile_expert"].numel()
     assert torch.equal(a["tile_pairs"][bound:], b["tile_pairs"][bound:])   # per-expert pair prefix
