@@ -232,16 +232,22 @@ def gate_up_key(sections):
     return None
 
 
-def parity_record(step_inputs, out, dx, w, idx, scores, weights, world, device, grad_out):
+def parity_record(x, out, dx, idx, scores, weights, grad_out, router_weight=None, topk=None):
     """Recompute a fixed sample of tokens (every 257th) with the fp32 oracle -- output and input gradient -- from the
     same bf16 inputs and routing decision; returns max |a-b| / max |b| for both.  ``weights`` = (w1, w2) holding ALL
-    experts in the order ``idx`` refers to."""
+    experts in the order ``idx`` refers to.  With ``router_weight`` the router is part of the step: the scores are
+    re-derived from the sampled tokens in fp32 (softmax over the selected logits) so that the input gradient includes
+    the path through the router, as the timed step's does."""
     from oracle import moe_oracle as O
 
     T = out.size(0)
-    sample = torch.arange(0, T, 257, device=device)
-    xs = step_inputs[sample].float().requires_grad_()
-    ref = O.expert_compute(xs, scores[sample].float(), idx[sample], weights[0].detach(), weights[1].detach(), "swiglu")
+    sample = torch.arange(0, T, 257, device=out.device)
+    xs = x[sample].float().requires_grad_()
+    if router_weight is not None:
+        sc = torch.softmax(torch.gather(xs @ router_weight.detach().float(), -1, idx[sample]), -1)
+    else:
+        sc = scores[sample].float()
+    ref = O.expert_compute(xs, sc, idx[sample], weights[0].detach(), weights[1].detach(), "swiglu")
     ref.backward(grad_out[sample].float())
     rel = lambda a, b: float((a.float() - b).abs().max() / b.abs().max().clamp_min(1e-30))
     return {"out": rel(out[sample], ref.detach()), "dx": rel(dx[sample], xs.grad), "tokens_checked": int(sample.numel())}
@@ -403,7 +409,7 @@ def run_ours(args):
         dist.all_gather_into_tensor(full[1], w2.detach())
         weights = full
     p_scores, p_idx = routing_of(x)
-    parity = parity_record(x, out, dx, w, p_idx, p_scores, weights, world, device, grad_out)
+    parity = parity_record(x, out, dx, p_idx, p_scores, weights, grad_out, inp["router_weight"] if with_router else None)
     del weights
     if world > 1:
         full = None
@@ -734,7 +740,7 @@ def report(args, name, w, world, ms, e2e, launches, tracer, clocks, with_router,
                                         "router distribution)" if world > 1 and args.placement == "balanced"
                                         else (args.placement if world > 1 else None)),
                    "row_gather": "inside the gate/up and weight1-gradient GEMMs' operand loads (tile::gather4)"
-                                 if args.gather_in_gemm != "off" and world == 1 else "separate copy kernel / peer pull",
+                                 if args.gather_in_gemm == "on" and world == 1 else "separate copy kernel / peer pull",
                    "l2": "inputs larger than L2 (expert weights are re-read from HBM every step)",
                    "flops_per_step": flops},
         "clocks": clocks,

@@ -36,9 +36,9 @@ class MGroupedGEMMParams:
 
 def m_grouped_gemm(token: torch.Tensor, params: MGroupedGEMMParams, autotune_mode=None) -> torch.Tensor:
     """Rows [g[e], g[e+1]) of the (optionally gathered) input times ``weight[e]``, optional activation epilogue,
-    optional scatter of the output rows.  As in the reference kernel the gather happens inside the GEMM's operand
-    loads and the scatter inside its epilogue (m_grouped_gemm.py:104-109, 168-172): no gathered copy of the input
-    and no un-scattered copy of the output exist."""
+    optional scatter of the output rows.  As in the reference kernel the scatter happens inside the GEMM's epilogue
+    (m_grouped_gemm.py:168-172): no un-scattered copy of the output exists.  The input rows are copied into
+    128-row-aligned expert segments first (one HBM-bound pass) so that the GEMM loads whole tiles."""
     assert token.dim() == 2
     assert params.weight.dim() == 3
     assert token.size(1) == params.weight.size(1)
@@ -67,15 +67,18 @@ def m_grouped_gemm(token: torch.Tensor, params: MGroupedGEMMParams, autotune_mod
     in_rows = flat_of_row if params.gather else plan.row_src     # input row of padded row p (before // div)
     in_div = params.topk if params.gather else 1
     out_rows = flat_of_row if params.scatter else plan.row_src   # output row of padded row p
+    # input rows into the padded layout with one copy kernel (the gather could ride on the GEMM's operand loads --
+    # mgrouped_gemm_gather -- but four-row gather copies are several times slower than 128-row tile copies)
+    a = torch.empty(plan.padded_rows, k_dim, dtype=token.dtype, device=token.device)
+    _native.gather_rows(token, in_rows, plan.num_mtiles, a, in_div)
     if not is_glu(act):
-        # element-wise epilogue: rows are gathered by the loads and scattered by the stores of the same kernel
-        _native.mgrouped_gemm_scatter(token, weight, out, out_rows, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
-                                      plan.padded_rows, False, act, a_row_src=in_rows, a_div=in_div, status=plan.status)
+        # element-wise epilogue: the rows are scattered to their final place by the stores of the GEMM itself
+        _native.mgrouped_gemm_scatter(a, weight, out, out_rows, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
+                                      plan.padded_rows, False, act, status=plan.status)
         return out
     # gated epilogue (two input columns per output column): output in the padded layout, then one un-pad pass
     y = torch.empty(plan.padded_rows, out_cols, dtype=token.dtype, device=token.device)
-    _native.mgrouped_gemm_gather(token, in_rows, in_div, weight, y, None, plan.mtile_expert, plan.tile_pairs,
-                                 plan.num_mtiles, plan.padded_rows, act, plan.status)
+    _native.mgrouped_gemm(a, weight, y, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, act, plan.status)
     if params.scatter:
         src_of_out = torch.empty(rows, dtype=torch.int32, device=token.device)
         src_of_out[params.permute_indices] = plan.dst_row   # out[perm[r]] = y[dst_row[r]]

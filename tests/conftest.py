@@ -11,6 +11,13 @@ for p in (os.path.join(ROOT, "moe-explore_b200"), ROOT):
 
 GOLDEN_DIR = os.path.join(ROOT, "tests", "golden")
 
+# MOE_TEST_GATHER_IN_GEMM=0/1 runs the whole suite with the other row-gather form of the layer (rows copied into the
+# expert-sorted layout first / gathered by the GEMMs' operand loads); unset = the package default.
+if os.environ.get("MOE_TEST_GATHER_IN_GEMM") in ("0", "1"):
+    import moe_explore.expert_compute as _ec
+
+    _ec.GATHER_IN_GEMM_DEFAULT = os.environ["MOE_TEST_GATHER_IN_GEMM"] == "1"
+
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")

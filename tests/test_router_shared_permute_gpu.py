@@ -97,13 +97,15 @@ def test_shared_expert_branch(num_shared, act, native):
                        SharedExpertParams(leaves[3], leaves[4], act))
     out = topk_moe_forward(leaves[0], params)
     out.backward(grad)
-    # oracle: routed part by the oracle's expert loop, shared part as the reference writes it
+    # oracle: routed part by the oracle's expert loop (scores re-derived in fp32 from the same selection, so that the
+    # input gradient includes the path through the router), shared part as the reference writes it
     from moe_explore.router import router
 
     with torch.no_grad():
-        scores, idx = router(x, params.router_params)
+        _, idx = router(x, params.router_params)
     f = [t.detach().float().requires_grad_() for t in (x, w1, w2, up, down)]
-    ref = O.expert_compute(f[0], scores.float(), idx, f[1], f[2], "swiglu")
+    scores = torch.softmax(torch.gather(f[0] @ wr.float(), -1, idx), -1)
+    ref = O.expert_compute(f[0], scores, idx, f[1], f[2], "swiglu")
     h = O.activation(f[0] @ f[3], act) @ f[4]
     ref = ref + h.sum(0)
     ref.backward(grad.float())
