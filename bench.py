@@ -451,6 +451,8 @@ def run_ours(args):
                                                            clocks=True, gather_in_gemm=gather_in_gemm)
         if not args.no_other_workloads:
             extras["other_workloads"] = other_workloads(device, gather_in_gemm)
+            extras["forward_variants"] = [forward_variants(n, WORKLOADS[n], device)
+                                          for n in ("qwen15_moe_a27b", "olmoe_8192")]
         if not args.no_gpu_baseline:
             extras["gpu_baseline"] = gpu_baseline(name)
         inp = x = None
@@ -603,6 +605,33 @@ def measure_single_gpu(name, w, device, steps, clocks=False, gather_in_gemm=None
         rec["section_ms_per_step"] = tracer.ms_per_step(extra)
     rec["status"] = check_device_status(device)
     del inp, w1, w2, x, g, logits
+    torch.cuda.empty_cache()
+    return rec
+
+
+def forward_variants(name, w, device, iters=10):
+    """Inference forward (no gradient) of workload ``w`` three ways: the default (row copy, GEMMs, deterministic fold),
+    with the fold fused into the down GEMM's epilogue (router weight x row added into the output by vector
+    reductions), and with the row gather fused into the gate/up GEMM's operand loads; ms each and the largest
+    deviation of the two fused forms from the default."""
+    from moe_explore.expert_compute import expert_compute
+    from moe_explore.routing_plan import build_routing_plan
+
+    inp = make_inputs(w, device)
+    x, w1, w2 = inp["x"], inp["w1"], inp["w2"]
+    with torch.no_grad():
+        scores, idx = scores_from_logits(inp["logits"], w["k"], x.dtype)
+        plan = build_routing_plan(idx, w["E"], w["k"], want_perm=False)
+        run = lambda **kw: expert_compute(x, scores, w1, w2, plan, "swiglu", **kw)
+        base = run(gather_in_gemm=False)
+        rec = {"workload": name, "tokens": w["T"], "forward_ms": event_ms(lambda: run(gather_in_gemm=False), iters)}
+        fused = run(gather_in_gemm=False, fused_combine=True)
+        rec["forward_fused_fold_ms"] = event_ms(lambda: run(gather_in_gemm=False, fused_combine=True), iters)
+        rec["fused_fold_vs_default"] = float((fused.float() - base.float()).abs().max() / base.float().abs().max())
+        gathered = run(gather_in_gemm=True)
+        rec["forward_fused_gather_ms"] = event_ms(lambda: run(gather_in_gemm=True), iters)
+        rec["fused_gather_equals_default"] = bool(torch.equal(gathered, base))
+    del inp, x, w1, w2
     torch.cuda.empty_cache()
     return rec
 
