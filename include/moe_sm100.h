@@ -224,6 +224,9 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  *   group_m       row units per scheduling group; 0 = default (12)
  *   align_experts 0 = library's choice, 1 / -1 = scheduling groups never / may span two experts
  *   single_cta    1 = one-SM kernels even when tile_pairs is given
+ *   separate_copies 1 = fetch every 64-column block of an N-contiguous operand tile with a copy of its own instead
+ *                 of one copy over a blocked view of the matrix (which needs the column count to be a multiple
+ *                 of 64 and is otherwise the default): for comparison measurements
  *   wave_counter  device word for the barrier's arrivals, zeroed by the call on `stream`; NULL = a slot of the
  *                 library's own ring (shared by all streams: a clash only costs a launch its barrier) */
 typedef struct moe_gemm_options {
@@ -233,8 +236,14 @@ typedef struct moe_gemm_options {
   int32_t group_m;
   int32_t align_experts;
   int32_t single_cta;
+  int32_t separate_copies;
+  int32_t reserved;
   uint32_t* wave_counter;
 } moe_gemm_options;
+
+/* sizeof(moe_gemm_options) as this library was built: lets a binding written in another language check its own
+ * declaration of the struct. */
+size_t moe_gemm_options_size(void);
 
 /* M-grouped: out = epilogue(a[rows of tile] @ w[expert of tile]).
  *   mtile_expert / tile_pairs / num_mtiles come from moe_routing_metadata; tile_pairs may be

@@ -97,6 +97,8 @@ extern "C" int moe_read_status(const int32_t* status, int32_t* code, int reset, 
   return MOE_OK;
 }
 
+extern "C" size_t moe_gemm_options_size(void) { return sizeof(moe_gemm_options); }
+
 extern "C" int moe_set_wait_limit_cycles(int64_t cycles) {
   g_wait_limit.store(cycles > 0 ? cycles : kDefaultWaitLimitCycles, std::memory_order_relaxed);
   return MOE_OK;

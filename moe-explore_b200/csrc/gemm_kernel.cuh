@@ -78,6 +78,11 @@ struct GemmArgs {
   int32_t m_dim;  // K-grouped: rows of each output matrix
   int32_t n_dim;  // accumulator columns (N of the contraction)
   int32_t k_dim;  // M-grouped: K of the contraction
+  // MN-major operands whose contiguous extent is a multiple of 64 are described to the copy engine as
+  // [blocks of 64][rows][64]: ONE copy per stage then fetches all the 64-element-wide column blocks of the tile
+  // (one instruction instead of two to four; the blocks land exactly where separate copies put them).
+  int32_t a_blocked;  // K-grouped A
+  int32_t b_blocked;  // B, when it is MN-major
   // A rows gathered by the loads (null: A is stored in the padded layout).  Padded row p reads row
   // a_row_src[p] / a_div of the A tensor, zeros where a_row_src[p] < 0.  a_rows = rows of the A tensor.
   const int32_t* a_row_src;
@@ -505,17 +510,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           } else if (remote) {
             if (KG) {
               const int krow = c.k_row0 + kb * BK;
-              if (!gather) {
+              if (gather) {
+              } else if (args.a_blocked) {
+                tma_load_3d_pair(sa, &tmap_a, 0, krow, c.m0 >> 6, fb, pol);
+              } else {
 #pragma unroll
                 for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * (BK * 128), &tmap_a, c.m0 + 64 * j, krow, fb, pol);
               }
+              if (args.b_blocked) {
+                tma_load_3d_pair(sb, &tmap_b, 0, krow, (c.n0 + bcol) >> 6, fb, pol);
+              } else {
 #pragma unroll
-              for (int j = 0; j < Plan::kBCols / 64; ++j)
-                tma_load_2d_pair(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, krow, fb, pol);
+                for (int j = 0; j < Plan::kBCols / 64; ++j)
+                  tma_load_2d_pair(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, krow, fb, pol);
+              }
             } else {
               if (!gather) tma_load_2d_pair(sa, &tmap_a, kb * BK, c.m0, fb, pol);
               if (B_K) {
                 tma_load_3d_pair(sb, &tmap_b, kb * BK, c.n0 + bcol, c.expert, fb, pol);
+              } else if (args.b_blocked) {
+                tma_load_4d_pair(sb, &tmap_b, 0, kb * BK, (c.n0 + bcol) >> 6, c.expert, fb, pol);
               } else {
 #pragma unroll
                 for (int j = 0; j < Plan::kBCols / 64; ++j)
@@ -526,17 +540,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
             // single CTA, or the leader of a pair: everything is local
             if (KG) {
               const int krow = c.k_row0 + kb * BK;
-              if (!gather) {
+              if (gather) {
+              } else if (args.a_blocked) {
+                tma_load_3d(sa, &tmap_a, 0, krow, c.m0 >> 6, fb, pol);
+              } else {
 #pragma unroll
                 for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * (BK * 128), &tmap_a, c.m0 + 64 * j, krow, fb, pol);
               }
+              if (args.b_blocked) {
+                tma_load_3d(sb, &tmap_b, 0, krow, (c.n0 + bcol) >> 6, fb, pol);
+              } else {
 #pragma unroll
-              for (int j = 0; j < Plan::kBCols / 64; ++j)
-                tma_load_2d(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, krow, fb, pol);
+                for (int j = 0; j < Plan::kBCols / 64; ++j)
+                  tma_load_2d(sb + j * (BK * 128), &tmap_b, c.n0 + bcol + 64 * j, krow, fb, pol);
+              }
             } else {
               if (!gather) tma_load_2d(sa, &tmap_a, kb * BK, c.m0, fb, pol);
               if (B_K) {
                 tma_load_3d(sb, &tmap_b, kb * BK, c.n0 + bcol, c.expert, fb, pol);
+              } else if (args.b_blocked) {
+                tma_load_4d(sb, &tmap_b, 0, kb * BK, (c.n0 + bcol) >> 6, c.expert, fb, pol);
               } else {
 #pragma unroll
                 for (int j = 0; j < Plan::kBCols / 64; ++j)

@@ -49,12 +49,15 @@ struct TmapKey {
   const void* ptr;
   int dtype;
   int rank;
-  uint64_t dims[3];
-  uint32_t box[3];
+  uint64_t dims[4];
+  uint64_t strides[3];  // bytes, of dims 1..rank-1
+  uint32_t box[4];
   bool operator==(const TmapKey& o) const {
     if (ptr != o.ptr || dtype != o.dtype || rank != o.rank) return false;
     for (int i = 0; i < rank; ++i)
       if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+    for (int i = 0; i + 1 < rank; ++i)
+      if (strides[i] != o.strides[i]) return false;
     return true;
   }
 };
@@ -64,16 +67,20 @@ static TmapKey g_tmap_keys[kTmapCacheSize];
 static CUtensorMap g_tmap_vals[kTmapCacheSize];
 static int g_tmap_used = 0, g_tmap_next = 0;
 
-// Tensor map over a row-major matrix (optionally batched): dims[0] is the contiguous one; 128-byte swizzle.
+// Tensor map with the 128-byte swizzle; dims[0] is the contiguous dimension.  `strides` (bytes, for dims 1..rank-1)
+// may be null for a dense row-major tensor.
 static int make_tmap(CUtensorMap* map, int dtype, const void* ptr, int rank, const uint64_t* dims,
-                     const uint32_t* box) {
+                     const uint32_t* box, const uint64_t* strides = nullptr) {
   TmapKey key{};
   key.ptr = ptr;
   key.dtype = dtype;
   key.rank = rank;
+  uint64_t dense = 2;
   for (int i = 0; i < rank; ++i) {
     key.dims[i] = dims[i];
     key.box[i] = box[i];
+    dense *= dims[i];
+    if (i < rank - 1) key.strides[i] = strides != nullptr ? strides[i] : dense;
   }
   {
     std::lock_guard<std::mutex> lock(g_tmap_mutex);
@@ -88,16 +95,14 @@ static int make_tmap(CUtensorMap* map, int dtype, const void* ptr, int rank, con
     set_error("cuTensorMapEncodeTiled is not available from the driver");
     return MOE_ERR_CUDA;
   }
-  cuuint64_t gdim[3];
-  cuuint64_t gstride[2];
-  cuuint32_t bdim[3];
-  cuuint32_t estr[3] = {1, 1, 1};
-  uint64_t stride = 2;
+  cuuint64_t gdim[4];
+  cuuint64_t gstride[3];
+  cuuint32_t bdim[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) {
     gdim[i] = dims[i];
     bdim[i] = box[i];
-    stride *= dims[i];
-    if (i < rank - 1) gstride[i] = stride;
+    if (i < rank - 1) gstride[i] = key.strides[i];
   }
   CUresult r = fn(map, dtype == MOE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
                   rank, const_cast<void*>(ptr), gdim, gstride, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -115,6 +120,17 @@ static int make_tmap(CUtensorMap* map, int dtype, const void* ptr, int rank, con
     g_tmap_vals[slot] = *map;
   }
   return MOE_OK;
+}
+
+// Blocked view of a [rows, cols] (x batch) matrix whose contiguous extent is a multiple of 64 elements:
+// dims {64, rows, cols / 64 (, batch)}, so that ONE copy with a {64, box_rows, blocks} box fetches `blocks` adjacent
+// 64-column blocks, each landing as a box_rows x 128-byte swizzled tile (the layout of separate 64-wide copies).
+static int make_tmap_blocked(CUtensorMap* map, int dtype, const void* ptr, uint64_t rows, uint64_t cols, uint64_t batch,
+                             uint32_t box_rows, uint32_t blocks) {
+  const uint64_t dims[4] = {64, rows, cols / 64, batch};
+  const uint64_t strides[3] = {cols * 2, 128, rows * cols * 2};
+  const uint32_t box[4] = {64, box_rows, blocks, 1};
+  return make_tmap(map, dtype, ptr, batch > 0 ? 4 : 3, dims, box, strides);
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -183,6 +199,9 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t a_rows, int K
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)N, (uint64_t)E};
     const uint32_t box[3] = {BK, (uint32_t)(BN / CTAS), 1};
     int rc = make_tmap(&tb, dtype, w, 3, dims, box);
+    if (rc != MOE_OK) return rc;
+  } else if (args.b_blocked) {
+    int rc = make_tmap_blocked(&tb, dtype, w, (uint64_t)K, (uint64_t)N, (uint64_t)E, BK, (uint32_t)(BN / CTAS / 64));
     if (rc != MOE_OK) return rc;
   } else {
     const uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)E};
@@ -256,6 +275,7 @@ static int mgrouped_common(const char* name, const void* a, const void* w, void*
   args.a_row_src = x.gather_row_src;
   args.a_div = x.gather_div;
   args.a_rows = static_cast<int32_t>(x.gather_rows);
+  args.b_blocked = (!w_transposed && N % 64 == 0 && o.separate_copies == 0) ? 1 : 0;
   args.out = out;
   args.aux_out = x.aux_out;
   args.aux_in = x.aux_in;
@@ -306,13 +326,19 @@ template <typename T, int BN, int CTAS>
 static int kgrouped_dispatch(const void* a, const void* b, int64_t a_rows, int64_t padded_rows, int M, int N,
                              const GemmArgs& args, int dtype, const LaunchParams& lp) {
   CUtensorMap ta, tb;
-  {
+  if (args.a_blocked) {
+    int rc = make_tmap_blocked(&ta, dtype, a, (uint64_t)a_rows, (uint64_t)M, 0, BK, BM / 64);
+    if (rc != MOE_OK) return rc;
+  } else {
     const uint64_t dims[2] = {(uint64_t)M, (uint64_t)a_rows};
     const uint32_t box[2] = {64, args.a_row_src != nullptr ? 1u : (uint32_t)BK};
     int rc = make_tmap(&ta, dtype, a, 2, dims, box);
     if (rc != MOE_OK) return rc;
   }
-  {
+  if (args.b_blocked) {
+    int rc = make_tmap_blocked(&tb, dtype, b, (uint64_t)padded_rows, (uint64_t)N, 0, BK, (uint32_t)(BN / CTAS / 64));
+    if (rc != MOE_OK) return rc;
+  } else {
     const uint64_t dims[2] = {(uint64_t)N, (uint64_t)padded_rows};
     const uint32_t box[2] = {64, BK};
     int rc = make_tmap(&tb, dtype, b, 2, dims, box);
@@ -346,6 +372,8 @@ static int kgrouped_common(const char* name, const void* a, int64_t gather_rows,
   args.a_row_src = gather_row_src;
   args.a_div = gather_div;
   args.a_rows = static_cast<int32_t>(gather_rows);
+  args.a_blocked = (gather_row_src == nullptr && M % 64 == 0 && o.separate_copies == 0) ? 1 : 0;
+  args.b_blocked = (N % 64 == 0 && o.separate_copies == 0) ? 1 : 0;
   args.out = dw;
   args.act = MOE_ACT_NONE;
   args.group_m = o.group_m > 0 ? o.group_m : kDefaultGroupM;

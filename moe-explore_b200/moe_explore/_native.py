@@ -29,7 +29,8 @@ STATUS_BAD_EXPERT_ID = 100
 class GemmOptions(ctypes.Structure):
     """``moe_gemm_options``: per-launch choices of the grouped GEMMs (zeros = the library's choices)."""
     _fields_ = [("max_ctas", c_int32), ("wave_sync", c_int32), ("wave_workers", c_int32), ("group_m", c_int32),
-                ("align_experts", c_int32), ("single_cta", c_int32), ("wave_counter", c_void_p)]
+                ("align_experts", c_int32), ("single_cta", c_int32), ("separate_copies", c_int32), ("reserved", c_int32),
+                ("wave_counter", c_void_p)]
 
 
 # name -> (restype, argtypes); the single source for both binding and the symbol-export test
@@ -40,6 +41,7 @@ SIGNATURES = {
     "moe_check_status": (c_int, [c_void_p, c_void_p]),
     "moe_read_status": (c_int, [c_void_p, POINTER(c_int32), c_int, c_void_p]),
     "moe_set_wait_limit_cycles": (c_int, [c_int64]),
+    "moe_gemm_options_size": (c_size_t, []),
     "moe_padded_rows_bound": (c_int64, [c_int64, c_int]),
     "moe_mtiles_bound": (c_int64, [c_int64, c_int]),
     "moe_routing_workspace_bytes": (c_size_t, [c_int64, c_int]),
@@ -125,6 +127,8 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = restype
             fn.argtypes = argtypes
+        if lib.moe_gemm_options_size() != ctypes.sizeof(GemmOptions):
+            raise ImportError(f"{LIB_PATH} was built with another layout of moe_gemm_options: rebuild it")
         _lib = lib
     return _lib
 
@@ -189,8 +193,8 @@ def set_wait_limit_cycles(cycles: int) -> None:
 
 
 def gemm_options(max_ctas: int = 0, wave_sync: int = 0, wave_workers: int = 0, group_m: int = 0, align_experts: int = 0,
-                 single_cta: int = 0, wave_counter=None) -> GemmOptions:
-    return GemmOptions(max_ctas, wave_sync, wave_workers, group_m, align_experts, single_cta,
+                 single_cta: int = 0, separate_copies: int = 0, wave_counter=None) -> GemmOptions:
+    return GemmOptions(max_ctas, wave_sync, wave_workers, group_m, align_experts, single_cta, separate_copies, 0,
                        None if wave_counter is None else wave_counter.data_ptr())
 
 

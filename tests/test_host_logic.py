@@ -96,3 +96,48 @@ def test_pipeline_schedule_partitions_the_local_experts(experts):
         if ctx.geometric and experts >= 32:
             first = experts * 1 // 32
             assert schedule[0] == (0, 32) and first <= experts // 8
+
+
+def test_status_codes_map_to_errors_and_warnings():
+    """The Python view of a device status word: 0 is fine, the wave barrier's fall-back is a warning (the launch's
+    results are valid), everything else raises."""
+    import warnings
+
+    from moe_explore import _native
+    from moe_explore.routing_plan import _report
+
+    assert _report(0) == 0
+    with warnings.catch_warnings(record=True) as seen:
+        warnings.simplefilter("always")
+        assert _report(_native.STATUS_WAVE_FALLBACK) == 4
+    assert len(seen) == 1 and "wave barrier" in str(seen[0].message)
+    for code, text in ((_native.STATUS_BAD_EXPERT_ID, "outside"), (_native.STATUS_BAD_LAYOUT, "does not describe"),
+                       (2, "bounded wait")):
+        with pytest.raises(_native.MoeNativeError, match=text):
+            _report(code)
+
+
+def test_options_struct_matches_the_library(native):
+    import ctypes
+
+    assert native.load().moe_gemm_options_size() == ctypes.sizeof(native.GemmOptions) == 40
+    o = native.gemm_options(max_ctas=140, wave_sync=-1, wave_workers=3)
+    assert (o.max_ctas, o.wave_sync, o.wave_workers, o.group_m, o.align_experts, o.single_cta, o.separate_copies,
+            o.wave_counter) == (140, -1, 3, 0, 0, 0, 0, None)
+
+
+def test_oracle_upcasts_narrower_weights_per_expert():
+    """The checker may hold 16-bit weights and compute in fp32: same result as upcasting everything first."""
+    import torch
+
+    from oracle import moe_oracle as O
+
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(40, 32, generator=g)
+    w1 = (torch.randn(4, 32, 48, generator=g) * 0.1).bfloat16()
+    w2 = (torch.randn(4, 24, 32, generator=g) * 0.1).bfloat16()
+    top, idx = torch.topk(torch.randn(40, 4, generator=g), 2, dim=-1)
+    s = torch.softmax(top, -1)
+    a = O.expert_compute(x, s, idx, w1, w2, "swiglu")
+    b = O.expert_compute(x, s, idx, w1.float(), w2.float(), "swiglu")
+    assert torch.equal(a, b)
