@@ -86,8 +86,13 @@ __device__ __forceinline__ bool peer_row_window(const int32_t* __restrict__ num_
 // dst[p, :] = scale[p] * bases[src_rank[p]][src_row[p], :], zeros where src_rank[p] < 0.  `bases` holds
 // one base pointer per rank of the node: the source rows live in peers' memory and are read with
 // ordinary 16-byte loads over NVLink (this GPU's own rows through the same path).
+// 128-thread CTAs of at most 64 registers: one of them still fits beside a grouped-GEMM CTA (320 threads x ~165
+// registers), so the pull also makes progress on the SMs it does not have to itself, and on a free SM eight fit.
+// The grid has more CTAs than can be resident; those that wait take over from the ones that finish, which hands
+// most rows to the SMs where the kernel runs fast.
+constexpr int kPeerThreads = 128;
 template <typename T>
-__global__ void __launch_bounds__(kRowThreads)
+__global__ void __launch_bounds__(kPeerThreads, 8)
 gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* __restrict__ src_rank,
                         const int32_t* __restrict__ src_row, const float* __restrict__ scale,
                         const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
@@ -95,39 +100,49 @@ gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* _
                         int vec_per_row) {
   int64_t row_begin, row_end;
   if (!peer_row_window(num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count, row_begin, row_end)) return;
-  for (int64_t p = row_begin + blockIdx.x; p < row_end; p += gridDim.x) {
-    const int32_t r = src_rank[p];
-    uint4* d = dst + p * vec_per_row;
-    if (r < 0) {
-      for (int v = threadIdx.x; v < vec_per_row; v += kRowThreads) d[v] = make_uint4(0, 0, 0, 0);
-      continue;
-    }
-    const uint4* s = bases[r] + static_cast<int64_t>(src_row[p]) * vec_per_row;
-    const float f = scale == nullptr ? 1.0f : scale[p];
-    // Four independent 16-byte loads per thread are issued before the first store: a remote load takes
-    // microseconds, and with load -> store -> load in program order a thread had only one in flight.
-    for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += 4 * kRowThreads) {
-      uint4 u[4];
+  // Two rows per iteration, up to four 16-byte loads per thread and row, ALL issued before the first store: a
+  // remote load takes microseconds, so what a thread keeps in flight is what the pull is worth (with one row of
+  // 7168 elements a thread had only 3.5 loads to issue; load -> store -> load in program order gave it one).
+  constexpr int kRows = 2, kLoads = 4;
+  for (int64_t p0 = row_begin + blockIdx.x; p0 < row_end; p0 += static_cast<int64_t>(gridDim.x) * kRows) {
+    for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += kLoads * kPeerThreads) {
+      uint4 u[kRows][kLoads];
+      float f[kRows];
+      bool live[kRows];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int v = v0 + i * kRowThreads;
-        u[i] = v < vec_per_row ? s[v] : make_uint4(0, 0, 0, 0);
+      for (int q = 0; q < kRows; ++q) {
+        const int64_t p = p0 + static_cast<int64_t>(q) * gridDim.x;
+        const int32_t r = p < row_end ? src_rank[p] : -1;
+        live[q] = r >= 0;
+        f[q] = (live[q] && scale != nullptr) ? scale[p] : 1.0f;
+        const uint4* s = live[q] ? bases[r] + static_cast<int64_t>(src_row[p]) * vec_per_row : nullptr;
+#pragma unroll
+        for (int i = 0; i < kLoads; ++i) {
+          const int v = v0 + i * kPeerThreads;
+          u[q][i] = (live[q] && v < vec_per_row) ? s[v] : make_uint4(0, 0, 0, 0);
+        }
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int v = v0 + i * kRowThreads;
-        if (v >= vec_per_row) continue;
-        if (scale != nullptr) {
-          const uint32_t w[4] = {u[i].x, u[i].y, u[i].z, u[i].w};
-          uint32_t o[4];
+      for (int q = 0; q < kRows; ++q) {
+        const int64_t p = p0 + static_cast<int64_t>(q) * gridDim.x;
+        if (p >= row_end) continue;
+        uint4* d = dst + p * vec_per_row;
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const float2 x = Elem<T>::unpack2(w[k]);
-            o[k] = Elem<T>::pack2(f * x.x, f * x.y);
+        for (int i = 0; i < kLoads; ++i) {
+          const int v = v0 + i * kPeerThreads;
+          if (v >= vec_per_row) continue;
+          if (live[q] && scale != nullptr) {
+            const uint32_t w[4] = {u[q][i].x, u[q][i].y, u[q][i].z, u[q][i].w};
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 x = Elem<T>::unpack2(w[k]);
+              o[k] = Elem<T>::pack2(f[q] * x.x, f[q] * x.y);
+            }
+            u[q][i] = make_uint4(o[0], o[1], o[2], o[3]);
           }
-          u[i] = make_uint4(o[0], o[1], o[2], o[3]);
+          d[v] = u[q][i];  // padding rows (src_rank < 0) are written as zeros
         }
-        d[v] = u[i];
       }
     }
   }
@@ -404,15 +419,15 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
   }
   // The load/store kernel is bound by NVLink, not by SMs, and usually runs beside a grouped GEMM: a few CTAs per SM
   // keep the links busy without taking issue slots from the GEMM.
-  const int64_t cap = static_cast<int64_t>(sm_count()) * 4;
+  const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int grid = static_cast<int>(padded_rows < cap ? padded_rows : cap);
   if (dtype == MOE_DTYPE_BF16) {
-    gather_rows_peer_kernel<__nv_bfloat16><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
+    gather_rows_peer_kernel<__nv_bfloat16><<<grid, kPeerThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
                                                                        tile_pairs, num_experts, mtiles_bound,
                                                                        chunk_index, chunk_count,
                                                                        static_cast<uint4*>(dst), cols / 8);
   } else {
-    gather_rows_peer_kernel<__half><<<grid, kRowThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
+    gather_rows_peer_kernel<__half><<<grid, kPeerThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
                                                                 num_experts, mtiles_bound, chunk_index, chunk_count,
                                                                 static_cast<uint4*>(dst), cols / 8);
   }

@@ -252,9 +252,11 @@ class EPContext:
         # of pull kernels per step with every SM busy, 14.1 ms with 8 SMs free, the GEMMs no slower since they
         # are power-limited).  Nothing to gain with one rank: local rows arrive fast either way.
         self.reserved_sms = 8 if self.world > 1 else 0
-        # How rows are pulled: "bulk" = the copy-engine kernel (one CTA on each reserved SM, ~170 KB of remote reads
-        # in flight per SM), "ldst" = the load/store kernel spread over all SMs (64 KB in flight per SM).
-        self.pull_mode = "bulk"
+        # How rows are pulled: "ldst" = the load/store kernel spread over all SMs (it also crawls along on the SMs that
+        # run GEMM CTAs), "bulk" = the copy-engine kernel, one CTA on each reserved SM.  Measured at 2 ranks with 8
+        # reserved SMs: 12.6 ms of pulls per step with "ldst", 29.5 ms with "bulk" (15.1 ms with 16 SMs): a warp of the
+        # bulk kernel has one row in flight at a time and only the reserved SMs work.
+        self.pull_mode = "ldst"
         if allocate:
             self._allocate_symmetric()
 
