@@ -453,6 +453,9 @@ def run_ours(args):
             extras["other_workloads"] = other_workloads(device, gather_in_gemm)
             extras["forward_variants"] = [forward_variants(n, WORKLOADS[n], device)
                                           for n in ("qwen15_moe_a27b", "olmoe_8192")]
+            extras["bmm_yardstick"] = [bmm_yardstick(n, WORKLOADS[n], device) for n in ("mixtral_8x7b", "olmoe_8192")]
+            if args.csv:
+                write_csv(args.csv, extras["other_workloads"])
         if not args.no_gpu_baseline:
             extras["gpu_baseline"] = gpu_baseline(name)
         inp = x = None
@@ -636,6 +639,39 @@ def forward_variants(name, w, device, iters=10):
     return rec
 
 
+def bmm_yardstick(name, w, device, iters=10):
+    """The reference harness's yardstick (bench/bench_m_grouped_gemm.py:156-159): with perfectly balanced routing the
+    ragged grouped GEMM is a batched GEMM, so ``torch.bmm`` (cuBLAS) on [E, R/E, K] x [E, K, N] bounds what a grouped
+    kernel can reach.  Times the gate/up contraction (no activation) both ways on the same operands."""
+    from moe_explore import _native
+    from moe_explore.routing_plan import build_routing_plan
+    from moe_explore.testing import perfect_routing
+
+    T, d, E, k, I = w["T"], w["d"], w["E"], w["k"], w["I"]
+    if (T * k) % (E * 128) != 0:
+        return {"workload": name, "skipped": "rows per expert are not a multiple of the 128-row tile"}
+    gen = torch.Generator(device=device).manual_seed(5)
+    _, idx = perfect_routing(T, E, k, device, torch.bfloat16)
+    plan = build_routing_plan(idx, E, k, want_perm=False)
+    rows = T * k
+    w1 = (torch.randn(E, d, 2 * I, generator=gen, device=device) * 0.02).bfloat16()
+    xs = torch.zeros(plan.padded_rows, d, dtype=torch.bfloat16, device=device)
+    xs[:rows] = torch.randn(rows, d, generator=gen, device=device).bfloat16()   # balanced: no padding inside experts
+    out = torch.empty(plan.padded_rows, 2 * I, dtype=torch.bfloat16, device=device)
+    ours = event_ms(lambda: _native.mgrouped_gemm(xs, w1, out, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
+                                                   False, None, plan.status), iters)
+    a3 = xs[:rows].view(E, rows // E, d)
+    ref = torch.bmm(a3, w1)
+    same = bool(torch.equal(ref.view(rows, -1), out[:rows]))
+    lib = event_ms(lambda: torch.bmm(a3, w1), iters)
+    flops = 4.0 * rows * d * I
+    rec = {"workload": name, "rows_per_expert": rows // E, "grouped_gemm_ms": ours, "grouped_gemm_tflops": flops / ours / 1e9,
+           "torch_bmm_ms": lib, "torch_bmm_tflops": flops / lib / 1e9, "bit_identical": same}
+    del w1, xs, out, ref
+    torch.cuda.empty_cache()
+    return rec
+
+
 def other_workloads(device, gather_in_gemm):
     """The remaining single-GPU configurations, device-resident, 10 steps each: the Qwen1.5-MoE layer, the OLMoE layer
     at 8192 tokens and the routing-stress sweep (4 token counts x 3 router distributions; the two small token counts
@@ -650,6 +686,19 @@ def other_workloads(device, gather_in_gemm):
                 rec["ms_per_step_cuda_graph"] = graph["ms_per_step"]
             out.append(rec)
     return out
+
+
+def write_csv(path, records):
+    """The single-GPU workload table as CSV (one row per configuration), for plotting next to the reference's
+    perf_report output."""
+    import csv
+
+    cols = ["workload", "tokens", "router", "ms_per_step", "ms_per_step_cuda_graph", "tflops", "frac_bf16_peak"]
+    with open(path, "w", newline="") as f:
+        out = csv.writer(f)
+        out.writerow(cols)
+        for r in records:
+            out.writerow([r.get(c, "") for c in cols])
 
 
 def gpu_baseline(name):
@@ -956,6 +1005,7 @@ def main():
                     help="N = 1: skip the extra measurement of the expert-parallel workload on one GPU")
     ap.add_argument("--no-other-workloads", action="store_true",
                     help="N = 1: skip the Qwen1.5-MoE / OLMoE / routing-stress-sweep measurements")
+    ap.add_argument("--csv", default=None, help="N = 1: also write the other-workloads table to this CSV file")
     ap.add_argument("--no-gpu-baseline", action="store_true",
                     help="N = 1: skip timing the reference's Triton kernels (needs a checkout of the reference)")
     ap.add_argument("--gather-in-gemm", default="auto", choices=["auto", "on", "off"],

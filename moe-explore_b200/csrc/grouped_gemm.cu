@@ -376,7 +376,14 @@ static int kgrouped_common(const char* name, const void* a, int64_t gather_rows,
   args.b_blocked = (N % 64 == 0 && o.separate_copies == 0) ? 1 : 0;
   args.out = dw;
   args.act = MOE_ACT_NONE;
-  args.group_m = o.group_m > 0 ? o.group_m : kDefaultGroupM;
+  {
+    // Row units (256 output rows per CTA pair) that share a sweep over the column tiles.  When an expert's whole
+    // first operand (rows x M) is at most ~24 units wide it stays in L2 for the sweep, and taking all units as ONE
+    // group reads the second operand (rows x N, the big one for the weight1 gradient) from HBM once instead of once
+    // per group.
+    const int units = (M + 2 * BM - 1) / (2 * BM);
+    args.group_m = o.group_m > 0 ? o.group_m : (units <= 24 ? units : kDefaultGroupM);
+  }
   args.wait_limit = wait_limit_cycles();
   args.status = status;
   LaunchParams lp;

@@ -1,5 +1,7 @@
 """Host-side pieces that need no GPU: parameter bundles, the activation enum, router dispatch,
 weight interleaving, and the differentiable torch cross-check of the layer."""
+import math
+
 import pytest
 import torch
 
@@ -141,3 +143,40 @@ def test_oracle_upcasts_narrower_weights_per_expert():
     a = O.expert_compute(x, s, idx, w1, w2, "swiglu")
     b = O.expert_compute(x, s, idx, w1.float(), w2.float(), "swiglu")
     assert torch.equal(a, b)
+
+
+def test_harness_routings_and_tolerance_rule():
+    """The harness helpers (routing generators, group cuts, tolerance rule) on the CPU: shapes, value ranges and the
+    properties their names promise."""
+    import torch
+
+    from moe_explore import testing as H
+
+    dev, dt = torch.device("cpu"), torch.float32
+    torch.manual_seed(0)
+    s, i = H.perfect_routing(64, 8, 2, dev, dt)
+    assert s.shape == (64, 2) and i.shape == (64, 2)
+    assert torch.bincount(i.reshape(-1), minlength=8).tolist() == [16] * 8
+    s, i = H.random_routing(100, 16, 4, dev, dt)
+    assert i.dtype == torch.int64 and int(i.min()) >= 0 and int(i.max()) < 16
+    assert all(len(set(row)) == 4 for row in i.tolist())                    # k distinct experts per token
+    s, i = H.random_skewed_routing(4000, 16, 2, num_skewed_experts=2, skew_factor=8, device=dev, dtype=dt)
+    counts = torch.bincount(i.reshape(-1), minlength=16).float()
+    top2 = counts.sort(descending=True).values[:2].sum()
+    assert top2 > 0.4 * counts.sum()                                        # two experts draw 16 of 30 weight units
+    p = H.zipf_popularity(64, 1.5, torch.Generator().manual_seed(1))
+    assert abs(float(p.sum()) - 1.0) < 1e-5 and float(p.max() / p.min()) > 400
+    s, i = H.popularity_routing(500, p, 8, dev, dt)
+    assert all(len(set(row)) == 8 for row in i.tolist())
+    g = H.random_groups(1000, 7, dev)
+    assert g.dtype == torch.int32 and g[0] == 0 and g[-1] == 1000 and bool((g[1:] > g[:-1]).all())
+    w = H.uniform_weight_init((4, 32, 64), dev, dt)
+    assert float(w.abs().max()) <= math.sqrt(3) * math.sqrt(2 / 96) + 1e-6
+    mlp = H.random_mlp(4, 32, 48, "swiglu", dev, dt)
+    assert mlp.weight1.shape == (4, 32, 96) and mlp.weight2.shape == (4, 48, 32)
+    a = torch.ones(8, 256, dtype=torch.bfloat16)
+    atol, rtol = H.tolerances(a, a)
+    assert atol == min(1e-2, 256 * 1.0 * 0.0078125 * 1e-2) and abs(rtol - 16 * 0.0078125 * 0.1) < 1e-12
+    H.assert_close(a, a)
+    with pytest.raises(AssertionError):
+        H.assert_close(a, a * 1.5)
