@@ -227,6 +227,9 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  *   separate_copies 1 = fetch every 64-column block of an N-contiguous operand tile with a copy of its own instead
  *                 of one copy over a blocked view of the matrix (which needs the column count to be a multiple
  *                 of 64 and is otherwise the default): for comparison measurements
+ *   lane_stores   1 = output tiles in the padded layout are written with 16-byte stores by the lanes instead of bulk
+ *                 tensor stores from the staging tile (the default when the column count is a multiple of 64): for
+ *                 comparison measurements
  *   wave_counter  device word for the barrier's arrivals, zeroed by the call on `stream`; NULL = a slot of the
  *                 library's own ring (shared by all streams: a clash only costs a launch its barrier) */
 typedef struct moe_gemm_options {
@@ -237,7 +240,7 @@ typedef struct moe_gemm_options {
   int32_t align_experts;
   int32_t single_cta;
   int32_t separate_copies;
-  int32_t reserved;
+  int32_t lane_stores;
   uint32_t* wave_counter;
 } moe_gemm_options;
 

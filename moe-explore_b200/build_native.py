@@ -1,6 +1,6 @@
 """Build libmoe_sm100.so in-tree with nvcc for sm_100a (cross-compiles without a GPU).
 
-Usage: python moe-explore_b200/build_native.py [--force]
+Usage: python moe-explore_b200/build_native.py [--force] [-v] [--out other/path.so]
 """
 from __future__ import annotations
 
@@ -32,7 +32,9 @@ def _stale(target: str, deps) -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
+def build(force: bool = False, verbose: bool = False, out: str = OUT) -> str:
+    """Compile what is stale and link ``out`` (default: the library next to the package; another path gives a second
+    build that ``MOE_SM100_LIBRARY`` can point the package at)."""
     sources = [os.path.join(CSRC, s) for s in SOURCES if os.path.exists(os.path.join(CSRC, s))]
     objs = []
     procs = []
@@ -48,14 +50,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {src}:\n{out}")
         if verbose:
             print(out)
-    if force or procs or _stale(OUT, objs):
-        cmd = [_nvcc(), "-shared", "-o", OUT] + objs
-        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if force or procs or _stale(out, objs):
+        # link into a temporary name and rename: a process that loads the library while it is being rebuilt sees the
+        # old file or the new one, never a partial one (nvcc's link step has also been seen to fail sporadically
+        # right after a batch of parallel compiles: one retry)
+        tmp = out + ".tmp"
+        cmd = [_nvcc(), "-shared", "-o", tmp] + objs
+        for attempt in range(2):
+            r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            if r.returncode == 0:
+                break
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}")
-    return OUT
+        os.replace(tmp, out)
+    return out
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    target = sys.argv[sys.argv.index("--out") + 1] if "--out" in sys.argv else OUT
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, out=target)
     print(path)

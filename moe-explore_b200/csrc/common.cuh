@@ -245,6 +245,11 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
                ::"l"(map), "r"(c0), "r"(c1), "r"(src)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_3d(const CUtensorMap* map, int c0, int c1, int c2, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(src)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Wait until the bulk stores committed by this thread have finished READING shared memory (the buffer may be reused).
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }

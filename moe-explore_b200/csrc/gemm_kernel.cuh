@@ -89,6 +89,7 @@ struct GemmArgs {
   int32_t a_div;
   int32_t a_rows;
   // epilogue
+  int32_t out_tma;     // EPI_ACT without a row map: tiles leave through bulk tensor stores (tmap_d covers `out`)
   void* out;           // EPI_ACT: [rows, N]; EPI_GLU: [rows, N/2]; EPI_DGLU: [rows, 2N]
   void* aux_out;       // EPI_GLU, EPI_ACT_AUX: un-activated product [rows, N] or null
   const void* aux_in;  // EPI_DGLU: saved un-activated product [rows, 2N]; EPI_ACT_AUX: the same, [rows, N], or null
@@ -354,8 +355,9 @@ __device__ __forceinline__ int4 gather_rows4(const int32_t* row_src, int first, 
   return r;
 }
 
-// tmap_a / tmap_b: the operands.  tmap_c / tmap_d (EPI_DGLU only): the saved product and the output, both
-// [rows, 2N] with a {64 columns, 32 rows} box.
+// tmap_a / tmap_b: the operands.  tmap_c / tmap_d (EPI_DGLU): the saved product and the output, both
+// [rows, 2N] with a {64 columns, 32 rows} box.  tmap_d (EPI_ACT with out_tma): the output, [rows, N] or
+// [E, M, N], same box.
 template <typename T, int BN, bool A_K, bool B_K, int EPI, bool KG, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -405,10 +407,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     mbar_fence_init();
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
-    if (EPI == EPI_DGLU) {
-      tma_prefetch_desc(&tmap_c);
-      tma_prefetch_desc(&tmap_d);
-    }
+    if (EPI == EPI_DGLU) tma_prefetch_desc(&tmap_c);
+    if (EPI == EPI_DGLU || (EPI == EPI_ACT && args.out_tma)) tma_prefetch_desc(&tmap_d);
   }
   if (warp == 1) {
     if (kPair) {
@@ -743,6 +743,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         const unsigned long long my_aux = two_outputs ? reinterpret_cast<unsigned long long>(aux_out + out_row * N) : 0ull;
         const int first_pass = two_outputs ? 0 : 1;
         const bool accumulate = EPI == EPI_ACT && !KG && args.combine_row_src != nullptr;
+        // Without a row map the 32-row x 64-column piece this warp has staged leaves as ONE bulk tensor store (the copy
+        // engine clips it at the edges of the matrix) instead of eight 16-byte stores per lane; the staging tile is
+        // written again only after that store has read it.
+        const bool tma_out = EPI == EPI_ACT && args.out_tma != 0;
+        const bool tile_stored = KG ? (c.m0 + quad * 32 < args.m_dim) : c.active;
 #pragma unroll 1
         for (int chunk = chunk_begin; chunk < chunk_begin + kChunksPerWarp; chunk += 2) {
 #pragma unroll 1
@@ -783,6 +788,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
 #pragma unroll
                 for (int i = 0; i < 32; ++i) v[i] *= row_scale;
               }
+              if (tma_out && hc == 0) {
+                if (lane == 0) bulk_wait_read_all();  // the previous round's store has read the staging tile
+                __syncwarp();
+              }
 #pragma unroll
               for (int qq = 0; qq < 4; ++qq) {
                 const uint4 u = pack8<T>(v + qq * 8);
@@ -791,8 +800,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                              : "memory");
               }
             }
-            __syncwarp();
             const int col_pair0 = c.n0 + chunk * 32;  // first of the 64 columns staged
+            if (tma_out) {
+              fence_proxy_async_smem();
+              __syncwarp();
+              if (lane == 0 && tile_stored && col_pair0 < N) {
+                if (KG) tma_store_3d(&tmap_d, col_pair0, c.m0 + quad * 32, c.expert, stage_base);
+                else tma_store_2d(&tmap_d, col_pair0, static_cast<int>(warp_row0), stage_base);
+                bulk_commit();
+              }
+              continue;
+            }
+            __syncwarp();
             const unsigned long long pass_base = pass == 0 ? my_aux : my_base;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -992,7 +1011,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (++acc == 2) { acc = 0; acc_phase ^= 1; }
       }
     }
-    if (EPI == EPI_DGLU && lane == 0) bulk_wait_all();  // this warp's stores have left shared memory and are complete
+    if ((EPI == EPI_DGLU || EPI == EPI_ACT) && lane == 0) bulk_wait_all();  // this warp's bulk stores are complete
   }
 
   tc_fence_before();

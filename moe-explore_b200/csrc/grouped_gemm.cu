@@ -210,8 +210,15 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t a_rows, int K
     if (rc != MOE_OK) return rc;
   }
   if (epi == EPI_ACT) {
-    return w_transposed ? launch<T, BN, true, true, EPI_ACT, false, CTAS>(ta, tb, ta, ta, args, lp)
-                        : launch<T, BN, true, false, EPI_ACT, false, CTAS>(ta, tb, ta, ta, args, lp);
+    CUtensorMap td = ta;
+    if (args.out_tma) {
+      const uint64_t dims[2] = {(uint64_t)N, (uint64_t)(args.mtiles_bound) * BM};
+      const uint32_t box[2] = {64, 32};
+      int rc = make_tmap(&td, dtype, args.out, 2, dims, box);
+      if (rc != MOE_OK) return rc;
+    }
+    return w_transposed ? launch<T, BN, true, true, EPI_ACT, false, CTAS>(ta, tb, ta, td, args, lp)
+                        : launch<T, BN, true, false, EPI_ACT, false, CTAS>(ta, tb, ta, td, args, lp);
   } else if (epi == EPI_GLU) {
     return launch<T, BN, true, false, EPI_GLU, false, CTAS>(ta, tb, ta, ta, args, lp);
   } else if (epi == EPI_ACT_AUX) {
@@ -276,6 +283,9 @@ static int mgrouped_common(const char* name, const void* a, const void* w, void*
   args.a_div = x.gather_div;
   args.a_rows = static_cast<int32_t>(x.gather_rows);
   args.b_blocked = (!w_transposed && N % 64 == 0 && o.separate_copies == 0) ? 1 : 0;
+  // plain stores in the padded layout leave through bulk tensor stores (64-column boxes: N a multiple of 64)
+  args.out_tma = (epi == EPI_ACT && x.push_row == nullptr && x.combine_row_src == nullptr && out != nullptr && N % 64 == 0 &&
+                  o.lane_stores == 0) ? 1 : 0;
   args.out = out;
   args.aux_out = x.aux_out;
   args.aux_in = x.aux_in;
@@ -344,7 +354,14 @@ static int kgrouped_dispatch(const void* a, const void* b, int64_t a_rows, int64
     int rc = make_tmap(&tb, dtype, b, 2, dims, box);
     if (rc != MOE_OK) return rc;
   }
-  return launch<T, BN, false, false, EPI_ACT, true, CTAS>(ta, tb, ta, ta, args, lp);
+  CUtensorMap td = ta;
+  if (args.out_tma) {
+    const uint64_t dims[3] = {(uint64_t)N, (uint64_t)M, (uint64_t)args.num_experts};
+    const uint32_t box[3] = {64, 32, 1};
+    int rc = make_tmap(&td, dtype, args.out, 3, dims, box);
+    if (rc != MOE_OK) return rc;
+  }
+  return launch<T, BN, false, false, EPI_ACT, true, CTAS>(ta, tb, ta, td, args, lp);
 }
 
 static int kgrouped_common(const char* name, const void* a, int64_t gather_rows, const int32_t* gather_row_src,
@@ -374,16 +391,10 @@ static int kgrouped_common(const char* name, const void* a, int64_t gather_rows,
   args.a_rows = static_cast<int32_t>(gather_rows);
   args.a_blocked = (gather_row_src == nullptr && M % 64 == 0 && o.separate_copies == 0) ? 1 : 0;
   args.b_blocked = (N % 64 == 0 && o.separate_copies == 0) ? 1 : 0;
+  args.out_tma = (N % 64 == 0 && o.lane_stores == 0) ? 1 : 0;
   args.out = dw;
   args.act = MOE_ACT_NONE;
-  {
-    // Row units (256 output rows per CTA pair) that share a sweep over the column tiles.  When an expert's whole
-    // first operand (rows x M) is at most ~24 units wide it stays in L2 for the sweep, and taking all units as ONE
-    // group reads the second operand (rows x N, the big one for the weight1 gradient) from HBM once instead of once
-    // per group.
-    const int units = (M + 2 * BM - 1) / (2 * BM);
-    args.group_m = o.group_m > 0 ? o.group_m : (units <= 24 ? units : kDefaultGroupM);
-  }
+  args.group_m = o.group_m > 0 ? o.group_m : kDefaultGroupM;
   args.wait_limit = wait_limit_cycles();
   args.status = status;
   LaunchParams lp;

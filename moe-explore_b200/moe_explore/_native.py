@@ -29,7 +29,7 @@ STATUS_BAD_EXPERT_ID = 100
 class GemmOptions(ctypes.Structure):
     """``moe_gemm_options``: per-launch choices of the grouped GEMMs (zeros = the library's choices)."""
     _fields_ = [("max_ctas", c_int32), ("wave_sync", c_int32), ("wave_workers", c_int32), ("group_m", c_int32),
-                ("align_experts", c_int32), ("single_cta", c_int32), ("separate_copies", c_int32), ("reserved", c_int32),
+                ("align_experts", c_int32), ("single_cta", c_int32), ("separate_copies", c_int32), ("lane_stores", c_int32),
                 ("wave_counter", c_void_p)]
 
 
@@ -193,8 +193,8 @@ def set_wait_limit_cycles(cycles: int) -> None:
 
 
 def gemm_options(max_ctas: int = 0, wave_sync: int = 0, wave_workers: int = 0, group_m: int = 0, align_experts: int = 0,
-                 single_cta: int = 0, separate_copies: int = 0, wave_counter=None) -> GemmOptions:
-    return GemmOptions(max_ctas, wave_sync, wave_workers, group_m, align_experts, single_cta, separate_copies, 0,
+                 single_cta: int = 0, separate_copies: int = 0, lane_stores: int = 0, wave_counter=None) -> GemmOptions:
+    return GemmOptions(max_ctas, wave_sync, wave_workers, group_m, align_experts, single_cta, separate_copies, lane_stores,
                        None if wave_counter is None else wave_counter.data_ptr())
 
 

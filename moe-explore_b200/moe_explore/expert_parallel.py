@@ -361,8 +361,11 @@ class NativePeerOps(NativeOps):
         return build_routing_plan(local_expert_ids, num_local_experts, 1, want_perm=False)
 
     def publish(self, ctx: EPContext, rows: torch.Tensor):
+        # An element-wise kernel, not a memcpy: a device-to-device memcpy may be queued on a copy engine behind a long
+        # host transfer of another stream (a training loop that uploads the next batch while this step runs), and
+        # everything after the publish waits for it.
         with _native.timed("ep:publish"):
-            ctx.src.copy_(rows)
+            torch.mul(rows, 1, out=ctx.src)
 
     def barrier(self, ctx: EPContext):
         """Stream-ordered: every rank's work enqueued so far is complete before any rank continues."""

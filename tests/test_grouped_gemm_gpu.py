@@ -375,7 +375,8 @@ def test_one_copy_per_operand_tile_equals_one_copy_per_column_block(N, native):
     """N-contiguous operand tiles are fetched with ONE copy over a blocked view of the matrix when the column count is
     a multiple of 64 (the default), or with one copy per 64-column block (``separate_copies``): the bytes land in the
     same places, so every output is bit-identical -- gate/up-style GEMM, plain GEMM, and the K-grouped contraction
-    (both operands N-contiguous), also where the last 256-column tile is ragged."""
+    (both operands N-contiguous), also where the last 256-column tile is ragged.  Likewise output tiles in the padded
+    layout leave through bulk tensor stores (the default) or through 16-byte stores of the lanes (``lane_stores``)."""
     plan, x, w, g = _small_problem(native, 31 + N, N=N, T=900)
     rp = plan.padded_rows
     n = int(plan.num_mtiles[0].item()) * 128
@@ -383,8 +384,8 @@ def test_one_copy_per_operand_tile_equals_one_copy_per_column_block(N, native):
     native.dispatch_rows(x, plan.dst_row, plan.row_src, plan.num_mtiles, xs, 1)
     b = torch.randn(rp, N, generator=g).to(torch.bfloat16).cuda() * (plan.row_src >= 0)[:, None]
     outs = []
-    for separate in (0, 1):
-        opts = native.gemm_options(separate_copies=separate)
+    for separate, lane_stores in ((0, 0), (1, 0), (0, 1)):   # default / one copy per column block / 16-byte lane stores
+        opts = native.gemm_options(separate_copies=separate, lane_stores=lane_stores)
         y = torch.zeros(rp, N, dtype=x.dtype, device="cuda")
         native.mgrouped_gemm(xs, w, y, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, None, plan.status,
                              options=opts)
@@ -395,8 +396,9 @@ def test_one_copy_per_operand_tile_equals_one_copy_per_column_block(N, native):
         native.kgrouped_gemm(xs, b, dw, plan.pad_offsets, plan.status, options=opts)
         outs.append((y[:n].clone(), h[:n].clone(), pre[:n].clone(), dw))
     plan.check()
-    for a_, b_ in zip(*outs):
-        assert torch.equal(a_, b_)
+    for other in outs[1:]:
+        for a_, b_ in zip(outs[0], other):
+            assert torch.equal(a_, b_)
     ref = torch.stack([xs[plan.pad_offsets[e]:plan.pad_offsets[e + 1]].float().t() @ b[plan.pad_offsets[e]:plan.pad_offsets[e + 1]].float()
                        for e in range(w.size(0))])
     assert relerr(outs[0][3], ref) <= TOL

@@ -125,7 +125,7 @@ def test_options_struct_matches_the_library(native):
     assert native.load().moe_gemm_options_size() == ctypes.sizeof(native.GemmOptions) == 40
     o = native.gemm_options(max_ctas=140, wave_sync=-1, wave_workers=3)
     assert (o.max_ctas, o.wave_sync, o.wave_workers, o.group_m, o.align_experts, o.single_cta, o.separate_copies,
-            o.wave_counter) == (140, -1, 3, 0, 0, 0, 0, None)
+            o.lane_stores, o.wave_counter) == (140, -1, 3, 0, 0, 0, 0, 0, None)
 
 
 def test_oracle_upcasts_narrower_weights_per_expert():
