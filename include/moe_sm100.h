@@ -151,6 +151,13 @@ int moe_layout_from_groups(const int32_t* group_indices, int64_t num_rows, int n
                            int32_t* mtile_expert, int32_t* tile_pairs, int32_t* num_mtiles,
                            int32_t* status, void* stream);
 
+/* Copies `bytes` (a multiple of 8) from device memory to PAGE-LOCKED host memory with a kernel that stores through
+ * the unified address space, asynchronously on `stream`; the host reads the buffer after synchronising the stream.
+ * For the small host reads of a step (expert-parallel split sizes): a cudaMemcpy of a few hundred bytes is queued on
+ * a copy engine behind any large host transfer another stream has in flight there, and measured a whole
+ * read-back (18-48 ms) of delay per step; a kernel store is not.  No counterpart in the reference. */
+int moe_store_to_host(const void* src, void* dst_pinned_host, size_t bytes, void* stream);
+
 /* ---------------------------------------------------------------------------------
  * Row movement (HBM-bound).  Replace row_gather / row_scatter
  * (triton_kernels/row_gather_scatter.py:36-116) and scale_and_reduce

@@ -45,21 +45,17 @@ def build(force: bool = False, verbose: bool = False, out: str = OUT) -> str:
             cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", src, "-o", obj]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     for src, p in procs:
-        out, _ = p.communicate()
+        log, _ = p.communicate()
         if p.returncode != 0:
-            raise RuntimeError(f"nvcc failed on {src}:\n{out}")
+            raise RuntimeError(f"nvcc failed on {src}:\n{log}")
         if verbose:
-            print(out)
+            print(log)
     if force or procs or _stale(out, objs):
         # link into a temporary name and rename: a process that loads the library while it is being rebuilt sees the
-        # old file or the new one, never a partial one (nvcc's link step has also been seen to fail sporadically
-        # right after a batch of parallel compiles: one retry)
+        # old file or the new one, never a partial one
         tmp = out + ".tmp"
         cmd = [_nvcc(), "-shared", "-o", tmp] + objs
-        for attempt in range(2):
-            r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-            if r.returncode == 0:
-                break
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}")
         os.replace(tmp, out)

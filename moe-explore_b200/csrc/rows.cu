@@ -331,6 +331,17 @@ combine_bwd_kernel(const uint4* __restrict__ dout, const T* __restrict__ scores,
   }
 }
 
+// A few words from device memory into PINNED host memory, written by a kernel through the unified address space.
+// For the one small host read a step needs (split sizes): a memcpy would be queued on a copy engine, behind
+// whatever large host transfer another stream has in flight there (the next batch's upload, the last result's
+// read-back), and the step would wait for all of it.
+__global__ void store_words_to_host_kernel(const unsigned long long* __restrict__ src, unsigned long long* __restrict__ dst,
+                                           int64_t words) {
+  for (int64_t i = blockIdx.x * blockDim.x + threadIdx.x; i < words; i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+    dst[i] = src[i];
+  __threadfence_system();
+}
+
 static int row_grid(int64_t rows) {
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   return static_cast<int>(rows < cap ? (rows > 0 ? rows : 1) : cap);
@@ -349,6 +360,23 @@ using namespace moe;
     return MOE_ERR_UNSUPPORTED;                                                                          \
   }                                                                                                      \
   MOE_CHECK_ARG((dtype) == MOE_DTYPE_BF16 || (dtype) == MOE_DTYPE_F16, name ": unknown dtype %d", (dtype))
+
+extern "C" int moe_store_to_host(const void* src, void* dst_pinned_host, size_t bytes, void* stream) {
+  MOE_CHECK_ARG(src != nullptr && dst_pinned_host != nullptr, "moe_store_to_host: null pointer argument");
+  MOE_CHECK_ARG(bytes % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 7u) == 0 &&
+                    (reinterpret_cast<uintptr_t>(dst_pinned_host) & 7u) == 0,
+                "moe_store_to_host: size and pointers must be multiples of 8 bytes");
+  if (bytes == 0) return MOE_OK;
+  cudaPointerAttributes attr;
+  MOE_CUDA(cudaPointerGetAttributes(&attr, dst_pinned_host));
+  MOE_CHECK_ARG(attr.type == cudaMemoryTypeHost, "moe_store_to_host: the destination is not page-locked host memory");
+  const int64_t words = static_cast<int64_t>(bytes / 8);
+  const int blocks = static_cast<int>(words < 256 * 64 ? (words + 255) / 256 : 64);
+  store_words_to_host_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned long long*>(src), static_cast<unsigned long long*>(attr.devicePointer), words);
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}
 
 extern "C" int moe_gather_rows(const void* src, int64_t src_rows, const int32_t* row_src, const int32_t* num_mtiles,
                                void* dst, int64_t padded_rows, int cols, int div, int dtype, void* stream) {

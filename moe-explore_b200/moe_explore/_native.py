@@ -50,6 +50,7 @@ SIGNATURES = {
     "moe_routing_metadata_static": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 9 + [c_void_p]),
     "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 7 + [c_void_p]),
     "moe_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "moe_store_to_host": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p,
                                      c_void_p]),
@@ -258,6 +259,29 @@ def router_topk(logits, topk: int, softmax_before_topk: bool, normalize: bool, w
     _check("moe_router_topk", rc)
     _count(1)
     return scores, indices, counts
+
+
+_PINNED = {}
+
+
+def read_small(values: torch.Tensor) -> list:
+    """The int64 values of a small CUDA tensor as a Python list: ONE host synchronisation, and no memcpy -- a kernel
+    stores the words into a cached page-locked buffer (a memcpy would queue on a copy engine behind large host
+    transfers of other streams).  CPU tensors are simply converted."""
+    if not values.is_cuda:
+        return values.tolist()
+    assert values.dtype is torch.int64
+    flat = values.reshape(-1).contiguous()
+    key = (flat.device.index, flat.numel())
+    host = _PINNED.get(key)
+    if host is None:
+        host = torch.empty(max(flat.numel(), 1), dtype=torch.int64).pin_memory()
+        _PINNED[key] = host
+    rc = load().moe_store_to_host(_ptr(flat), host.data_ptr(), flat.numel() * 8, _stream())
+    _check("moe_store_to_host", rc)
+    _count(1)
+    torch.cuda.current_stream().synchronize()
+    return host[: flat.numel()].tolist()
 
 
 def gather_rows(src, row_src, num_mtiles, dst, div):

@@ -170,9 +170,9 @@ def build_dispatch_layout(indices: torch.Tensor, num_experts: int, group, ops) -
     recv_counts = torch.empty_like(send_counts)          # [source rank, local expert]
     dist.all_to_all_single(recv_counts, send_counts, group=group)
     status = ops.status_word(flat.device).to(torch.int64) if hasattr(ops, "status_word") else torch.zeros(1, dtype=torch.int64, device=flat.device)
-    host = torch.cat((send_counts.sum(1), recv_counts.sum(1), status)).cpu()   # the one host read of the step
-    _report(int(host[-1]))                                                     # e.g. an expert id out of range
-    send_splits, recv_splits = host[:world].tolist(), host[world:2 * world].tolist()
+    host = _native.read_small(torch.cat((send_counts.sum(1), recv_counts.sum(1), status)))   # the one host read of the step
+    _report(int(host[-1]))                                                                   # e.g. an expert id out of range
+    send_splits, recv_splits = host[:world], host[world:2 * world]
     local_ids = torch.arange(e_local, device=flat.device).repeat(world)
     local_expert_ids = torch.repeat_interleave(local_ids, recv_counts.reshape(-1), output_size=sum(recv_splits))
     inv = torch.empty(R, dtype=torch.int32, device=flat.device)
@@ -308,10 +308,10 @@ def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: 
     all_counts = gathered.view(world, num_experts)
     pair = all_counts.view(world, world, e_local).sum(-1)              # [source, owner] rows
     status = ops.status_word(dev).to(torch.int64) if hasattr(ops, "status_word") else torch.zeros(1, dtype=torch.int64, device=dev)
-    host_all = torch.cat((pair.reshape(-1), status)).cpu()             # the one host read of the step
-    _report(int(host_all[-1]))                                         # e.g. an expert id out of range
-    host = host_all[:-1].view(world, world)
-    send_splits, recv_splits = host[me].tolist(), host[:, me].tolist()
+    host_all = _native.read_small(torch.cat((pair.reshape(-1), status)))   # the one host read of the step
+    _report(int(host_all[-1]))                                             # e.g. an expert id out of range
+    send_splits = host_all[me * world:(me + 1) * world]
+    recv_splits = host_all[me:world * world:world]
     num_received = sum(recv_splits)
     send_base = pair.cumsum(1) - pair                                   # start of each owner's segment at the source
     base_on_source = send_base[:, me]                                   # [world]
