@@ -859,6 +859,14 @@ def report(args, name, w, world, ms, e2e, launches, tracer, clocks, with_router,
         line["config"]["load_imbalance_max_over_mean"] = round(max(rows_per_rank) / mean, 4) if mean else None
     if tracer.sections:
         line["section_ms_per_step"] = tracer.ms_per_step(args.steps)
+        for key in ("ep:wait_pull", "rows:gather_peer"):
+            # per pipeline chunk (forward chunks, then backward chunks): where the GEMM stream waits for rows
+            ev = tracer.sections.get(key)
+            if ev and len(ev) % args.steps == 0:
+                per = len(ev) // args.steps
+                line.setdefault("per_chunk_ms", {})[key] = [
+                    round(sum(ev[s_ * per + c][0].elapsed_time(ev[s_ * per + c][1]) for s_ in range(args.steps)) / args.steps, 3)
+                    for c in range(per)]
     line.update(extras)
     print(json.dumps(line), flush=True)
 

@@ -182,7 +182,8 @@ int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* ro
  * one base pointer per rank of the node (peer-mapped buffers of [*, cols] rows, e.g. symmetric memory);
  * rows are read with ordinary loads over NVLink.  scale (fp32, may be NULL) is applied in fp32.
  * chunk_count > 1 restricts the call to the rows of the experts [E*chunk_index/chunk_count,
- * E*(chunk_index+1)/chunk_count) (see moe_mgrouped_gemm); tile_pairs and num_experts are needed then.
+ * E*(chunk_index+1)/chunk_count) (see moe_mgrouped_gemm); chunk_count < 0 selects the explicit expert range
+ * [chunk_index, -chunk_count) instead; tile_pairs and num_experts are needed for either.
  * bulk_ctas > 0 selects the copy-engine kernel on that many CTAs (one per SM that is free for it): every warp
  * moves whole rows with cp.async.bulk through a shared-memory slot, which keeps ~170 KB of remote reads in
  * flight per SM; bulk_ctas == 0 selects the load/store kernel spread over all SMs.
@@ -237,6 +238,9 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  *   lane_stores   1 = output tiles in the padded layout are written with 16-byte stores by the lanes instead of bulk
  *                 tensor stores from the staging tile (the default when the column count is a multiple of 64): for
  *                 comparison measurements
+ *   expert_begin, expert_end  M-grouped kernels: when end > begin, process exactly the experts [begin, end) (needs
+ *                 tile_pairs); overrides chunk_index / chunk_count.  Lets a caller cut the expert list into slices
+ *                 of unequal size, e.g. by row counts
  *   wave_counter  device word for the barrier's arrivals, zeroed by the call on `stream`; NULL = a slot of the
  *                 library's own ring (shared by all streams: a clash only costs a launch its barrier) */
 typedef struct moe_gemm_options {
@@ -248,6 +252,8 @@ typedef struct moe_gemm_options {
   int32_t single_cta;
   int32_t separate_copies;
   int32_t lane_stores;
+  int32_t expert_begin;
+  int32_t expert_end;
   uint32_t* wave_counter;
 } moe_gemm_options;
 

@@ -108,6 +108,8 @@ struct GemmArgs {
   int32_t act;
   int32_t chunk_index;  // M-grouped: process only the experts [E*index/count, E*(index+1)/count) (lets a caller
   int32_t chunk_count;  // pipeline row movement against the GEMM); count <= 1 = everything
+  int32_t expert_begin;  // M-grouped: when expert_end > expert_begin, process exactly the experts [begin, end)
+  int32_t expert_end;    // instead (slices of unequal size, e.g. chosen by row counts)
   int32_t align_experts;  // M-grouped CTA pairs: scheduling groups never span two experts
   uint32_t* wave_counter;  // non-null: workers start every work item together (grid-wide arrival counter, zeroed
                            // by the host before the launch)
@@ -210,7 +212,10 @@ __device__ __forceinline__ int total_tiles(const GemmArgs& args, int& mt, int& n
       mt = 0;
       return 0;
     }
-    if (args.chunk_count > 1) {
+    if (args.expert_end > args.expert_begin) {
+      win.e0 = args.expert_begin;
+      win.e1 = args.expert_end < args.num_experts ? args.expert_end : args.num_experts;
+    } else if (args.chunk_count > 1) {
       win.e0 = static_cast<int>(static_cast<long long>(args.num_experts) * args.chunk_index / args.chunk_count);
       win.e1 = static_cast<int>(static_cast<long long>(args.num_experts) * (args.chunk_index + 1) / args.chunk_count);
     }

@@ -263,6 +263,11 @@ static int mgrouped_common(const char* name, const void* a, const void* w, void*
   GemmArgs args{};
   args.chunk_index = x.chunk_index;
   args.chunk_count = x.chunk_count;
+  MOE_CHECK_ARG(o.expert_end <= o.expert_begin || (tile_pairs != nullptr && o.expert_begin >= 0 && o.expert_begin < E),
+                "%s: the expert range [%d, %d) needs tile_pairs and 0 <= begin < num_experts", name, o.expert_begin,
+                o.expert_end);
+  args.expert_begin = o.expert_begin;
+  args.expert_end = o.expert_end;
   args.mtile_expert = mtile_expert;
   args.tile_pairs = tile_pairs;
   args.mtiles_bound = static_cast<int32_t>(padded_rows / BM);

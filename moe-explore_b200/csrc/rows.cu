@@ -65,17 +65,24 @@ dispatch_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ 
 // Row window of a pull: everything, or the rows of the experts of chunk `chunk_index` of `chunk_count` (the same
 // slicing the grouped GEMMs use, so a caller can pipeline the pull of chunk c+1 against the GEMMs of chunk c).
 // False when the metadata was built for another padded row count.
+// chunk_count < 0 encodes an explicit expert range: experts [chunk_index, -chunk_count).
 __device__ __forceinline__ bool peer_row_window(const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
                                                 int num_experts, int mtiles_bound, int chunk_index, int chunk_count,
                                                 int64_t& row_begin, int64_t& row_end) {
   row_begin = 0;
   row_end = static_cast<int64_t>(num_mtiles[0]) * MOE_TILE_M;
-  if (chunk_count > 1) {
+  if (chunk_count > 1 || chunk_count < 0) {
     if (num_mtiles[2] != mtiles_bound) return false;
     const int32_t* pair_prefix = tile_pairs + mtiles_bound;
     const int pairs = num_mtiles[1];
-    const int e0 = static_cast<int>(static_cast<long long>(num_experts) * chunk_index / chunk_count);
-    const int e1 = static_cast<int>(static_cast<long long>(num_experts) * (chunk_index + 1) / chunk_count);
+    int e0, e1;
+    if (chunk_count < 0) {
+      e0 = chunk_index;
+      e1 = -chunk_count < num_experts ? -chunk_count : num_experts;
+    } else {
+      e0 = static_cast<int>(static_cast<long long>(num_experts) * chunk_index / chunk_count);
+      e1 = static_cast<int>(static_cast<long long>(num_experts) * (chunk_index + 1) / chunk_count);
+    }
     const int p0 = pair_prefix[e0], p1 = pair_prefix[e1];
     if (p1 < pairs) row_end = static_cast<int64_t>(tile_pairs[p1] & 0xFFFFF) * MOE_TILE_M;
     row_begin = p0 < pairs ? static_cast<int64_t>(tile_pairs[p0] & 0xFFFFF) * MOE_TILE_M : row_end;
@@ -414,8 +421,10 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
   MOE_CHECK_ARG(peer_bases && src_rank && src_row && num_mtiles && dst, "moe_gather_rows_peer: null pointer argument");
   MOE_CHECK_ARG(aligned16(dst), "moe_gather_rows_peer: dst must be 16-byte aligned");
   MOE_CHECK_ARG(padded_rows > 0, "moe_gather_rows_peer: bad sizes");
-  MOE_CHECK_ARG(chunk_count <= 1 || (tile_pairs != nullptr && num_experts > 0 && chunk_index >= 0 && chunk_index < chunk_count),
-                "moe_gather_rows_peer: chunk %d of %d needs tile_pairs, num_experts and 0 <= index < count", chunk_index,
+  MOE_CHECK_ARG((chunk_count >= 0 && chunk_count <= 1) ||
+                    (tile_pairs != nullptr && num_experts > 0 && chunk_index >= 0 &&
+                     (chunk_count > 1 ? chunk_index < chunk_count : chunk_index < -chunk_count && chunk_index < num_experts)),
+                "moe_gather_rows_peer: chunk %d of %d needs tile_pairs, num_experts and a valid slice", chunk_index,
                 chunk_count);
   const int mtiles_bound = static_cast<int>(padded_rows / MOE_TILE_M);
   MOE_ROW_COMMON_CHECKS("moe_gather_rows_peer", cols, dtype);

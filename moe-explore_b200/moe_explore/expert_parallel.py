@@ -54,20 +54,48 @@ def balanced_placement(expert_load, world: int) -> torch.Tensor:
     expert e's weights at position ``remap[e]``.
 
     Greedy longest-processing-time assignment with a per-rank capacity: experts in decreasing load order,
-    each to the least-loaded rank that still has a free slot."""
+    each to the least-loaded rank that still has a free slot; inside a rank the positions go by increasing load."""
     load = [float(v) for v in (expert_load.tolist() if hasattr(expert_load, "tolist") else expert_load)]
     num_experts = len(load)
     assert num_experts % world == 0, "experts must divide evenly over the ranks"
     cap = num_experts // world
     total = [0.0] * world
-    used = [0] * world
-    remap = [0] * num_experts
+    owned = [[] for _ in range(world)]
     for e in sorted(range(num_experts), key=lambda i: (-load[i], i)):
-        r = min((g for g in range(world) if used[g] < cap), key=lambda g: (total[g], g))
-        remap[e] = r * cap + used[r]
-        used[r] += 1
+        r = min((g for g in range(world) if len(owned[g]) < cap), key=lambda g: (total[g], g))
+        owned[r].append(e)
         total[r] += load[e]
+    remap = [0] * num_experts
+    for r in range(world):
+        # within a rank: lightest expert first.  The expert-parallel pipeline starts its GEMMs as soon as the rows of
+        # the first experts have arrived, so the first slice should be small, and a hot expert (under a Zipf router one
+        # expert can hold 40 % of a rank's rows) should come last, when there is earlier work to hide its pull under.
+        for slot, e in enumerate(sorted(owned[r], key=lambda i: (load[i], i))):
+            remap[e] = r * cap + slot
     return torch.tensor(remap, dtype=torch.int64)
+
+
+def pipeline_schedule(rows_per_expert, first_fraction: float = 1.0 / 32, growth: float = 2.0, max_slices: int = 8):
+    """Slices [begin, end) of the local expert list, in launch order, for pipelining the pull of slice c+1 against the
+    GEMMs of slice c.  The pulls run back to back from the start of the pass, so slice c can start computing when a
+    fraction f_c of all rows has arrived; with pulls P and GEMMs G per pass (P < G) nothing waits after the first
+    slice as long as every slice holds at most G/P times the rows before it.  Hence: a first slice of about
+    ``first_fraction`` of the rows (its pull is the only one nothing hides), then slices of at most ``growth`` times
+    the rows already scheduled -- cut by ROWS, which under a skewed router is far from cutting by expert count."""
+    rows = [int(v) for v in rows_per_expert]
+    n, total = len(rows), sum(rows)
+    if n <= 1 or total == 0:
+        return [(0, n)]
+    slices, begin, done = [], 0, 0
+    target = max(total * first_fraction, 1.0)
+    for e in range(n - 1):
+        done += rows[e]
+        if done >= target and len(slices) < max_slices - 1:
+            slices.append((begin, e + 1))
+            begin = e + 1
+            target = done * (1.0 + growth)
+    slices.append((begin, n))
+    return slices
 
 
 class NativeOps:
@@ -244,8 +272,8 @@ class EPContext:
         self.num_tokens, self.hidden, self.topk, self.dtype, self.device = num_tokens, hidden, topk, dtype, device
         self.rows_up = _round_up(max(num_tokens * topk, 1), 128)
         self.busy = False
-        self.chunks = 8          # slices of the local expert list pipelined between the pull and the GEMMs
-        self.geometric = True    # growing slices (see NativePeerOps._chunks) instead of `chunks` equal ones
+        self.chunks = 8          # equal slices of the local expert list, used when `geometric` is off
+        self.geometric = True    # slices cut by received rows, small first and growing (pipeline_schedule)
         self.comm_stream = None  # side stream the pulls run on (created with the buffers)
         # SMs the grouped GEMMs leave free while rows are pulled from peers (read by the native ops): a pull CTA
         # that shares an SM with a GEMM CTA gets almost none of the SM's L2 ingress (measured at 2 ranks: 37.8 ms
@@ -291,6 +319,7 @@ class PeerLayout:
     p_dest: torch.Tensor          # int32 [RP]: row of that rank's y_back / dx_back this row is pushed to
     p_scale: torch.Tensor         # fp32  [RP]: router weight of the row (applied to dOut rows in backward)
     num_received: int
+    expert_rows: list = None      # rows received per local expert (host list; drives the pipeline schedule)
 
 
 def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: int, group, ops) -> PeerLayout:
@@ -308,10 +337,12 @@ def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: 
     all_counts = gathered.view(world, num_experts)
     pair = all_counts.view(world, world, e_local).sum(-1)              # [source, owner] rows
     status = ops.status_word(dev).to(torch.int64) if hasattr(ops, "status_word") else torch.zeros(1, dtype=torch.int64, device=dev)
-    host_all = _native.read_small(torch.cat((pair.reshape(-1), status)))   # the one host read of the step
+    local_rows = all_counts[:, me * e_local:(me + 1) * e_local].sum(0)       # rows each local expert receives
+    host_all = _native.read_small(torch.cat((pair.reshape(-1), local_rows, status)))   # the one host read of the step
     _report(int(host_all[-1]))                                             # e.g. an expert id out of range
     send_splits = host_all[me * world:(me + 1) * world]
     recv_splits = host_all[me:world * world:world]
+    expert_rows = host_all[world * world:world * world + e_local]
     num_received = sum(recv_splits)
     send_base = pair.cumsum(1) - pair                                   # start of each owner's segment at the source
     base_on_source = send_base[:, me]                                   # [world]
@@ -351,7 +382,7 @@ def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: 
     padded[:R] = perm.to(torch.int32)
     tiles = torch.full((1,), padded.numel() // 128, dtype=torch.int32, device=dev)
     return PeerLayout(padded, inv, tiles, plan, p_rank.contiguous(), p_tok.contiguous(), p_dest.contiguous(),
-                      p_scale.contiguous(), num_received)
+                      p_scale.contiguous(), num_received, expert_rows)
 
 
 class NativePeerOps(NativeOps):
@@ -379,28 +410,30 @@ class NativePeerOps(NativeOps):
 
     @staticmethod
     def _chunks(ctx: EPContext, lay: PeerLayout):
-        """Pipeline schedule: a list of (index, count) slices of the local expert list, in launch order.
-
-        With at least 32 local experts the slices grow geometrically -- 1/32, 1/32, 1/16, 1/8, 1/4, 1/2 of the
-        experts -- so that the first pull, which nothing hides, is a quarter of a uniform eighth (the waits for
-        pulls were 3.9 ms of a 70 ms step at 2 ranks with uniform eighths).  Every slice is still one
-        (chunk_index, chunk_count) pair of the native entry points: floor(E*2i/2c) == floor(E*i/c)."""
+        """Pipeline schedule: slices [begin, end) of the local expert list, in launch order.  By default they are cut
+        by the rows each local expert received (``pipeline_schedule``); ``ctx.geometric = False`` cuts ``ctx.chunks``
+        slices of equal expert count instead."""
         experts = lay.plan.num_experts
-        if ctx.geometric and experts >= 32:
-            return [(0, 32), (1, 32), (1, 16), (1, 8), (1, 4), (1, 2)]
+        if ctx.geometric and lay.expert_rows is not None and len(lay.expert_rows) == experts:
+            return pipeline_schedule(lay.expert_rows)
         n = max(1, min(ctx.chunks, experts))
-        return [(c, n) for c in range(n)]
+        return [(experts * c // n, experts * (c + 1) // n) for c in range(n) if experts * (c + 1) // n > experts * c // n]
+
+    @staticmethod
+    def _slice_rows(lay: PeerLayout, experts):
+        if lay.expert_rows is None:
+            return lay.num_received * (experts[1] - experts[0]) / max(lay.plan.num_experts, 1)
+        return sum(lay.expert_rows[experts[0]:experts[1]])
 
     @staticmethod
     def _sm_count(ctx: EPContext) -> int:
         return _native.query_device(ctx.device.index if ctx.device.index is not None else torch.cuda.current_device())[0]
 
     @classmethod
-    def _gemm_options(cls, ctx: EPContext):
-        """Launch options that leave ``ctx.reserved_sms`` SMs free for the pull kernels (None: no cap)."""
-        if ctx.reserved_sms <= 0:
-            return None
-        return _native.gemm_options(max_ctas=max(cls._sm_count(ctx) - ctx.reserved_sms, 2))
+    def _gemm_options(cls, ctx: EPContext, experts):
+        """Launch options of one pipeline slice: its experts, and ``ctx.reserved_sms`` SMs left free for the pulls."""
+        cap = max(cls._sm_count(ctx) - ctx.reserved_sms, 2) if ctx.reserved_sms > 0 else 0
+        return _native.gemm_options(max_ctas=cap, experts=experts)
 
     def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
         """Enqueue the pull of every chunk on the side stream; returns one event per chunk."""
@@ -415,8 +448,8 @@ class NativePeerOps(NativeOps):
         with torch.cuda.stream(ctx.comm_stream):
             for chunk in chunks:
                 _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, scale, plan.num_mtiles, dst,
-                                         plan.tile_pairs, plan.num_experts, chunk, bulk_ctas=bulk_ctas,
-                                         status=plan.status)
+                                         plan.tile_pairs, plan.num_experts, bulk_ctas=bulk_ctas, status=plan.status,
+                                         experts=chunk)
                 ev = torch.cuda.Event()
                 ev.record(ctx.comm_stream)
                 events.append(ev)
@@ -431,15 +464,14 @@ class NativePeerOps(NativeOps):
         xs, hidden, pre_act = new(rp, d), new(rp, weight2.size(1)), new(rp, weight1.size(2))
         main = torch.cuda.current_stream()
         events = self._pull_chunks(ctx, lay, None, xs)
-        capped = self._gemm_options(ctx)
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
+            opts, rows = self._gemm_options(ctx, chunk), self._slice_rows(lay, chunk)
             _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
-                                  False, act, plan.status, rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
+                                  False, act, plan.status, rows=rows, options=opts)
             _native.mgrouped_gemm_push(hidden, weight2, ctx.y_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
-                                       plan.tile_pairs, plan.num_mtiles, False, plan.status,
-                                       rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
+                                       plan.tile_pairs, plan.num_mtiles, False, plan.status, rows=rows, options=opts)
         return xs, hidden, pre_act
 
     def peer_backward(self, ctx: EPContext, lay: PeerLayout, state, weight1, weight2, act):
@@ -450,15 +482,14 @@ class NativePeerOps(NativeOps):
         gs, d_pre = new(rp, d), new(rp, pre_act.size(1))
         main = torch.cuda.current_stream()
         events = self._pull_chunks(ctx, lay, lay.p_scale, gs)      # score-scaled dOut rows
-        capped = self._gemm_options(ctx)
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
+            opts, rows = self._gemm_options(ctx, chunk), self._slice_rows(lay, chunk)
             _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
-                                       act, plan.status, rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
+                                       act, plan.status, rows=rows, options=opts)
             _native.mgrouped_gemm_push(d_pre, weight1, ctx.dx_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
-                                       plan.tile_pairs, plan.num_mtiles, True, plan.status,
-                                       rows=lay.num_received / chunk[1], chunk=chunk, options=capped)
+                                       plan.tile_pairs, plan.num_mtiles, True, plan.status, rows=rows, options=opts)
         # no pull runs beside the weight-gradient GEMMs: they use every SM
         d_w1 = torch.empty_like(weight1)
         _native.kgrouped_gemm(xs, d_pre, d_w1, plan.pad_offsets, plan.status, rows=lay.num_received, tag="dw1")

@@ -193,6 +193,39 @@ def test_chunked_launches_cover_every_tile_exactly_once(chunks, native):
     assert torch.equal(parts[:n], whole[:n]) and torch.equal(pre_parts[:n], pre_whole[:n])
 
 
+def test_explicit_expert_ranges_cover_every_tile_exactly_once(native):
+    """``moe_gemm_options.expert_begin / expert_end`` (slices of unequal size, as the expert-parallel pipeline cuts them
+    by rows) on the GEMMs, and the matching explicit range of the peer pull: the launches over a partition of the
+    expert list equal one launch over everything, bit for bit."""
+    from moe_explore.routing_plan import build_routing_plan
+
+    g = torch.Generator().manual_seed(5)
+    E, T, K, N = 11, 2500, 256, 512
+    idx = torch.randint(0, E, (T, 1), generator=g)
+    idx[idx == 4] = 3      # an expert without rows inside a slice
+    plan = build_routing_plan(idx.cuda(), E, 1)
+    n = int(plan.num_mtiles[0].item()) * 128
+    src = torch.randn(T, K, generator=g).to(torch.bfloat16).cuda()
+    bases = torch.tensor([src.data_ptr()], dtype=torch.int64, device="cuda")
+    p_rank = torch.where(plan.row_src >= 0, 0, -1).to(torch.int32)
+    p_row = plan.row_src.clamp_min(0).contiguous()
+    w = (torch.randn(E, K, N, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    whole_a = torch.full((plan.padded_rows, K), 7.0, dtype=torch.bfloat16, device="cuda")
+    native.gather_rows_peer(bases, p_rank, p_row, None, plan.num_mtiles, whole_a)
+    whole = torch.zeros(plan.padded_rows, N // 2, dtype=torch.bfloat16, device="cuda")
+    native.mgrouped_gemm(whole_a, w, whole, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, "swiglu", plan.status)
+    for bulk in (0, 16):
+        parts_a = torch.full_like(whole_a, 7.0)
+        parts = torch.zeros_like(whole)
+        for experts in ((0, 1), (1, 2), (2, 7), (7, 11)):
+            native.gather_rows_peer(bases, p_rank, p_row, None, plan.num_mtiles, parts_a, plan.tile_pairs, E, experts=experts,
+                                    bulk_ctas=bulk, status=plan.status)
+            native.mgrouped_gemm(parts_a, w, parts, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, "swiglu",
+                                 plan.status, options=native.gemm_options(experts=experts))
+        plan.check()
+        assert torch.equal(parts_a[:n], whole_a[:n]) and torch.equal(parts[:n], whole[:n])
+
+
 @pytest.mark.parametrize("limit", [2, 36, 140])
 def test_capped_grid_gives_the_same_result(limit, native):
     """``max_ctas`` of the launch options only changes how many persistent CTAs share the tiles (also for the long

@@ -79,25 +79,59 @@ def test_torch_cross_check_matches_oracle_and_is_differentiable():
 
 @pytest.mark.parametrize("experts", [1, 5, 31, 32, 33, 64, 100, 128, 1000])
 def test_pipeline_schedule_partitions_the_local_experts(experts):
-    """Every (chunk_index, chunk_count) slice covers experts [E*i/c, E*(i+1)/c) (integer division, the formula of the
-    native entry points); the slices of a schedule must tile [0, E) in launch order, without gaps or overlaps."""
+    """The slices of a pipeline schedule tile [0, E) in launch order, without gaps, overlaps or empty slices -- cut by
+    rows (the default), or into equal expert counts."""
     from types import SimpleNamespace
 
     from moe_explore.expert_parallel import NativePeerOps
 
-    lay = SimpleNamespace(plan=SimpleNamespace(num_experts=experts))
-    for ctx in (SimpleNamespace(chunks=8, geometric=True), SimpleNamespace(chunks=8, geometric=False),
-                SimpleNamespace(chunks=3, geometric=False)):
+    g = torch.Generator().manual_seed(experts)
+    rows = torch.randint(0, 2000, (experts,), generator=g).tolist()
+    for ctx, expert_rows in ((SimpleNamespace(chunks=8, geometric=True), rows), (SimpleNamespace(chunks=8, geometric=False), rows),
+                             (SimpleNamespace(chunks=3, geometric=False), None), (SimpleNamespace(chunks=8, geometric=True), None)):
+        lay = SimpleNamespace(plan=SimpleNamespace(num_experts=experts), expert_rows=expert_rows, num_received=sum(rows))
         schedule = NativePeerOps._chunks(ctx, lay)
         covered = 0
-        for index, count in schedule:
-            lo, hi = experts * index // count, experts * (index + 1) // count
-            assert lo == covered and hi >= lo
+        for lo, hi in schedule:
+            assert lo == covered and hi > lo
             covered = hi
-        assert covered == experts
-        if ctx.geometric and experts >= 32:
-            first = experts * 1 // 32
-            assert schedule[0] == (0, 32) and first <= experts // 8
+        assert covered == experts and len(schedule) <= 8
+
+
+def test_pipeline_schedule_is_cut_by_rows_not_by_expert_count():
+    """Under a skewed router the first slice must stay small and no slice may hold more than `growth` times the rows
+    scheduled before it (the condition under which only the first pull is exposed), unless a single expert is that
+    big by itself."""
+    from moe_explore.expert_parallel import balanced_placement, pipeline_schedule
+
+    g = torch.Generator().manual_seed(1)
+    E, world = 256, 4
+    p = (torch.arange(1, E + 1, dtype=torch.float64) ** -1.1)[torch.randperm(E, generator=g)]
+    u = torch.rand(32768, E, generator=g, dtype=torch.float64).clamp_min(1e-20)
+    idx = torch.topk(torch.log(p / p.sum()) - torch.log(-torch.log(u)), 8, dim=-1).indices
+    load = torch.bincount(idx.reshape(-1), minlength=E)
+    remap = balanced_placement(load, world)
+    e_local = E // world
+    for r in range(world):
+        # rows of the local experts in position order: ascending load inside a rank, the hot expert last
+        local = torch.zeros(e_local, dtype=torch.int64)
+        mine = (remap // e_local) == r
+        local[(remap[mine] % e_local)] = load[mine]
+        rows = local.tolist()
+        assert rows == sorted(rows)
+        total = sum(rows)
+        schedule = pipeline_schedule(rows)
+        assert schedule[0][0] == 0 and schedule[-1][1] == e_local
+        first = sum(rows[schedule[0][0]:schedule[0][1]])
+        assert first <= total / 32 + max(rows[:schedule[0][1]])          # about 1/32 of the rows, one expert of slack
+        done = first
+        for lo, hi in schedule[1:]:
+            here = sum(rows[lo:hi])
+            assert here <= 2.0 * done + rows[hi - 1] or hi - lo == 1 or (lo, hi) == schedule[-1]
+            done += here
+        assert done == total
+    assert pipeline_schedule([0, 0, 0]) == [(0, 3)] and pipeline_schedule([5]) == [(0, 1)]
+    assert pipeline_schedule([100] * 64, first_fraction=1 / 32) [0] == (0, 2)
 
 
 def test_status_codes_map_to_errors_and_warnings():
@@ -122,10 +156,10 @@ def test_status_codes_map_to_errors_and_warnings():
 def test_options_struct_matches_the_library(native):
     import ctypes
 
-    assert native.load().moe_gemm_options_size() == ctypes.sizeof(native.GemmOptions) == 40
+    assert native.load().moe_gemm_options_size() == ctypes.sizeof(native.GemmOptions) == 48
     o = native.gemm_options(max_ctas=140, wave_sync=-1, wave_workers=3)
     assert (o.max_ctas, o.wave_sync, o.wave_workers, o.group_m, o.align_experts, o.single_cta, o.separate_copies,
-            o.lane_stores, o.wave_counter) == (140, -1, 3, 0, 0, 0, 0, 0, None)
+            o.lane_stores, o.expert_begin, o.expert_end, o.wave_counter) == (140, -1, 3, 0, 0, 0, 0, 0, 0, 0, None)
 
 
 def test_oracle_upcasts_narrower_weights_per_expert():
