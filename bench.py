@@ -1019,7 +1019,7 @@ def main():
     ap.add_argument("--gather-in-gemm", default="auto", choices=["auto", "on", "off"],
                     help="single GPU: token rows gathered by the GEMMs' operand loads (auto = the package default) or "
                          "copied into the expert-sorted layout first")
-    ap.add_argument("--ep-pull", default="ldst", choices=["bulk", "ldst"],
+    ap.add_argument("--ep-pull", default="ldst", choices=["bulk", "ldst", "dedicated"],
                     help="N > 1, peer mode: pull rows with the copy-engine kernel on the reserved SMs or with the "
                          "load/store kernel on all SMs")
     ap.add_argument("--ep-reserved-sms", type=int, default=None,

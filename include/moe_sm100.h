@@ -186,13 +186,15 @@ int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* ro
  * [chunk_index, -chunk_count) instead; tile_pairs and num_experts are needed for either.
  * bulk_ctas > 0 selects the copy-engine kernel on that many CTAs (one per SM that is free for it): every warp
  * moves whole rows with cp.async.bulk through a shared-memory slot, which keeps ~170 KB of remote reads in
- * flight per SM; bulk_ctas == 0 selects the load/store kernel spread over all SMs.
+ * flight per SM; bulk_ctas == 0 selects the load/store kernel: spread over all SMs in 128-thread CTAs that also fit
+ * beside a GEMM CTA (dedicated_ctas == 0), or as dedicated_ctas CTAs of 1024 threads, each of which has an SM to
+ * itself (the caller keeps that many SMs free of GEMM CTAs with moe_gemm_options.max_ctas).
  * No counterpart in the reference (it is single-GPU). */
 int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank,
                          const int32_t* src_row, const float* scale, const int32_t* num_mtiles,
                          const int32_t* tile_pairs, int num_experts, int chunk_index,
                          int chunk_count, void* dst, int64_t padded_rows, int cols, int dtype,
-                         int bulk_ctas, int32_t* status, void* stream);
+                         int bulk_ctas, int dedicated_ctas, int32_t* status, void* stream);
 
 /* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order (zeros where
  * dst_row[j] < 0). */

@@ -97,9 +97,13 @@ __device__ __forceinline__ bool peer_row_window(const int32_t* __restrict__ num_
 // registers), so the pull also makes progress on the SMs it does not have to itself, and on a free SM eight fit.
 // The grid has more CTAs than can be resident; those that wait take over from the ones that finish, which hands
 // most rows to the SMs where the kernel runs fast.
-constexpr int kPeerThreads = 128;
-template <typename T>
-__global__ void __launch_bounds__(kPeerThreads, 8)
+//
+// THREADS = 1024 is the DEDICATED form: one CTA takes the whole register file of an SM, so it neither fits beside
+// a GEMM CTA nor lets one start next to it; launched with as many CTAs as the GEMMs leave SMs free, the pull then
+// has those SMs to itself (131 KB of loads in flight on each) and the GEMMs are not slowed by pull CTAs that share
+// their SMs' L2 ingress and issue slots.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS, THREADS == 128 ? 8 : 1)
 gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* __restrict__ src_rank,
                         const int32_t* __restrict__ src_row, const float* __restrict__ scale,
                         const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
@@ -112,7 +116,7 @@ gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* _
   // 7168 elements a thread had only 3.5 loads to issue; load -> store -> load in program order gave it one).
   constexpr int kRows = 2, kLoads = 4;
   for (int64_t p0 = row_begin + blockIdx.x; p0 < row_end; p0 += static_cast<int64_t>(gridDim.x) * kRows) {
-    for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += kLoads * kPeerThreads) {
+    for (int v0 = threadIdx.x; v0 < vec_per_row; v0 += kLoads * THREADS) {
       uint4 u[kRows][kLoads];
       float f[kRows];
       bool live[kRows];
@@ -125,7 +129,7 @@ gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* _
         const uint4* s = live[q] ? bases[r] + static_cast<int64_t>(src_row[p]) * vec_per_row : nullptr;
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
-          const int v = v0 + i * kPeerThreads;
+          const int v = v0 + i * THREADS;
           u[q][i] = (live[q] && v < vec_per_row) ? s[v] : make_uint4(0, 0, 0, 0);
         }
       }
@@ -136,7 +140,7 @@ gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* _
         uint4* d = dst + p * vec_per_row;
 #pragma unroll
         for (int i = 0; i < kLoads; ++i) {
-          const int v = v0 + i * kPeerThreads;
+          const int v = v0 + i * THREADS;
           if (v >= vec_per_row) continue;
           if (live[q] && scale != nullptr) {
             const uint32_t w[4] = {u[q][i].x, u[q][i].y, u[q][i].z, u[q][i].w};
@@ -416,8 +420,8 @@ extern "C" int moe_dispatch_rows(const void* src, const int32_t* dst_row, const 
 extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank, const int32_t* src_row,
                                     const float* scale, const int32_t* num_mtiles, const int32_t* tile_pairs,
                                     int num_experts, int chunk_index, int chunk_count, void* dst,
-                                    int64_t padded_rows, int cols, int dtype, int bulk_ctas, int32_t* status,
-                                    void* stream) {
+                                    int64_t padded_rows, int cols, int dtype, int bulk_ctas, int dedicated_ctas,
+                                    int32_t* status, void* stream) {
   MOE_CHECK_ARG(peer_bases && src_rank && src_row && num_mtiles && dst, "moe_gather_rows_peer: null pointer argument");
   MOE_CHECK_ARG(aligned16(dst), "moe_gather_rows_peer: dst must be 16-byte aligned");
   MOE_CHECK_ARG(padded_rows > 0, "moe_gather_rows_peer: bad sizes");
@@ -454,19 +458,33 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
     }
     // rows too long for a slot: fall through to the load/store kernel
   }
-  // The load/store kernel is bound by NVLink, not by SMs, and usually runs beside a grouped GEMM: a few CTAs per SM
-  // keep the links busy without taking issue slots from the GEMM.
+  if (dedicated_ctas > 0) {
+    // load/store kernel, one 1024-thread CTA on each SM the caller keeps free of GEMM CTAs
+    const int grid_d = dedicated_ctas < sm_count() ? dedicated_ctas : sm_count();
+    if (dtype == MOE_DTYPE_BF16) {
+      gather_rows_peer_kernel<__nv_bfloat16, 1024><<<grid_d, 1024, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
+                                                                         tile_pairs, num_experts, mtiles_bound, chunk_index,
+                                                                         chunk_count, static_cast<uint4*>(dst), cols / 8);
+    } else {
+      gather_rows_peer_kernel<__half, 1024><<<grid_d, 1024, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
+                                                                  num_experts, mtiles_bound, chunk_index, chunk_count,
+                                                                  static_cast<uint4*>(dst), cols / 8);
+    }
+    MOE_CUDA(cudaGetLastError());
+    return MOE_OK;
+  }
+  // The load/store kernel spread over all SMs: bound by NVLink, not by SMs; small CTAs keep the links busy and one of
+  // them still fits beside a grouped-GEMM CTA.
   const int64_t cap = static_cast<int64_t>(sm_count()) * 8;
   const int grid = static_cast<int>(padded_rows < cap ? padded_rows : cap);
   if (dtype == MOE_DTYPE_BF16) {
-    gather_rows_peer_kernel<__nv_bfloat16><<<grid, kPeerThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
-                                                                       tile_pairs, num_experts, mtiles_bound,
-                                                                       chunk_index, chunk_count,
-                                                                       static_cast<uint4*>(dst), cols / 8);
+    gather_rows_peer_kernel<__nv_bfloat16, 128><<<grid, 128, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
+                                                                    tile_pairs, num_experts, mtiles_bound, chunk_index,
+                                                                    chunk_count, static_cast<uint4*>(dst), cols / 8);
   } else {
-    gather_rows_peer_kernel<__half><<<grid, kPeerThreads, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
-                                                                num_experts, mtiles_bound, chunk_index, chunk_count,
-                                                                static_cast<uint4*>(dst), cols / 8);
+    gather_rows_peer_kernel<__half, 128><<<grid, 128, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
+                                                             num_experts, mtiles_bound, chunk_index, chunk_count,
+                                                             static_cast<uint4*>(dst), cols / 8);
   }
   MOE_CUDA(cudaGetLastError());
   return MOE_OK;

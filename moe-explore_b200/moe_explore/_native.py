@@ -53,8 +53,8 @@ SIGNATURES = {
     "moe_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "moe_store_to_host": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
-    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_void_p,
-                                     c_void_p]),
+    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                                     c_void_p, c_void_p]),
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_combine_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_combine_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
@@ -298,9 +298,10 @@ def gather_rows(src, row_src, num_mtiles, dst, div):
 
 
 def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst, tile_pairs=None, num_experts=0,
-                     chunk=(0, 1), bulk_ctas: int = 0, status=None, experts=None):
+                     chunk=(0, 1), bulk_ctas: int = 0, status=None, experts=None, dedicated_ctas: int = 0):
     """dst[p] = scale[p] * peer_bases[src_rank[p]][src_row[p]]; peer_bases: int64 device tensor of base pointers.
-    ``bulk_ctas`` > 0: the copy-engine kernel on that many CTAs; 0: the load/store kernel on all SMs.
+    ``bulk_ctas`` > 0: the copy-engine kernel on that many CTAs; 0: the load/store kernel, on all SMs or, with
+    ``dedicated_ctas`` > 0, as that many 1024-thread CTAs that each take a whole SM.
     ``experts`` = (begin, end) restricts the call to the rows of that slice of the expert list (else ``chunk``)."""
     require_cuda(peer_bases, dst)
     if experts is not None:
@@ -308,7 +309,8 @@ def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst, tile
     with timed("rows:gather_peer"):
         rc = load().moe_gather_rows_peer(_ptr(peer_bases), _ptr(src_rank), _ptr(src_row), _ptr(scale), _ptr(num_mtiles),
                                          _ptr(tile_pairs), num_experts, chunk[0], chunk[1], _ptr(dst), dst.size(0),
-                                         dst.size(1), dtype_code(dst.dtype), int(bulk_ctas), _ptr(status), _stream())
+                                         dst.size(1), dtype_code(dst.dtype), int(bulk_ctas), int(dedicated_ctas),
+                                         _ptr(status), _stream())
     _check("moe_gather_rows_peer", rc)
     _count(1)
 

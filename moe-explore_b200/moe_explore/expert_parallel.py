@@ -280,10 +280,11 @@ class EPContext:
         # of pull kernels per step with every SM busy, 14.1 ms with 8 SMs free, the GEMMs no slower since they
         # are power-limited).  Nothing to gain with one rank: local rows arrive fast either way.
         self.reserved_sms = 8 if self.world > 1 else 0
-        # How rows are pulled: "ldst" = the load/store kernel spread over all SMs (it also crawls along on the SMs that
-        # run GEMM CTAs), "bulk" = the copy-engine kernel, one CTA on each reserved SM.  Measured at 2 ranks with 8
-        # reserved SMs: 12.6 ms of pulls per step with "ldst", 29.5 ms with "bulk" (15.1 ms with 16 SMs): a warp of the
-        # bulk kernel has one row in flight at a time and only the reserved SMs work.
+        # How rows are pulled: "ldst" = the load/store kernel spread over all SMs (it also runs, slowly, on the SMs that
+        # run GEMM CTAs -- and slows those GEMMs), "dedicated" = the same kernel as one 1024-thread CTA on each reserved
+        # SM (it cannot share an SM with a GEMM CTA either way), "bulk" = the copy-engine kernel, one CTA on each
+        # reserved SM.  Measured at 2 ranks with 8 reserved SMs: 12.6 ms of pulls per step with "ldst", 29.5 ms with
+        # "bulk" (15.1 ms with 16 SMs): a warp of the bulk kernel has one row in flight at a time.
         self.pull_mode = "ldst"
         if allocate:
             self._allocate_symmetric()
@@ -430,9 +431,10 @@ class NativePeerOps(NativeOps):
         return _native.query_device(ctx.device.index if ctx.device.index is not None else torch.cuda.current_device())[0]
 
     @classmethod
-    def _gemm_options(cls, ctx: EPContext, experts):
-        """Launch options of one pipeline slice: its experts, and ``ctx.reserved_sms`` SMs left free for the pulls."""
-        cap = max(cls._sm_count(ctx) - ctx.reserved_sms, 2) if ctx.reserved_sms > 0 else 0
+    def _gemm_options(cls, ctx: EPContext, experts, last: bool):
+        """Launch options of one pipeline slice: its experts, and ``ctx.reserved_sms`` SMs left free for the pulls of
+        the slices after it (the last slice has no pull beside it and takes every SM)."""
+        cap = max(cls._sm_count(ctx) - ctx.reserved_sms, 2) if (ctx.reserved_sms > 0 and not last) else 0
         return _native.gemm_options(max_ctas=cap, experts=experts)
 
     def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
@@ -441,15 +443,17 @@ class NativePeerOps(NativeOps):
         main = torch.cuda.current_stream()
         ctx.comm_stream.wait_stream(main)          # the layout arrays and the destination exist
         # copy-engine pull: one CTA per reserved SM while GEMMs hold the others; every SM when nothing is reserved
-        bulk_ctas = 0
+        bulk_ctas = dedicated_ctas = 0
         if ctx.pull_mode == "bulk":
             bulk_ctas = ctx.reserved_sms if ctx.reserved_sms > 0 else self._sm_count(ctx)
+        elif ctx.pull_mode == "dedicated":
+            dedicated_ctas = ctx.reserved_sms if ctx.reserved_sms > 0 else self._sm_count(ctx)
         events = []
         with torch.cuda.stream(ctx.comm_stream):
             for chunk in chunks:
                 _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, scale, plan.num_mtiles, dst,
                                          plan.tile_pairs, plan.num_experts, bulk_ctas=bulk_ctas, status=plan.status,
-                                         experts=chunk)
+                                         experts=chunk, dedicated_ctas=dedicated_ctas)
                 ev = torch.cuda.Event()
                 ev.record(ctx.comm_stream)
                 events.append(ev)
@@ -467,7 +471,7 @@ class NativePeerOps(NativeOps):
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
-            opts, rows = self._gemm_options(ctx, chunk), self._slice_rows(lay, chunk)
+            opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), self._slice_rows(lay, chunk)
             _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
                                   False, act, plan.status, rows=rows, options=opts)
             _native.mgrouped_gemm_push(hidden, weight2, ctx.y_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
@@ -485,7 +489,7 @@ class NativePeerOps(NativeOps):
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
-            opts, rows = self._gemm_options(ctx, chunk), self._slice_rows(lay, chunk)
+            opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), self._slice_rows(lay, chunk)
             _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
                                        act, plan.status, rows=rows, options=opts)
             _native.mgrouped_gemm_push(d_pre, weight1, ctx.dx_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,

@@ -217,7 +217,7 @@ def test_balanced_placement_is_a_permutation_and_evens_the_load():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("pull_mode", ["bulk", "ldst"])   # copy-engine pull kernel / load-store pull kernel
+@pytest.mark.parametrize("pull_mode", ["bulk", "ldst", "dedicated"])   # the three pull kernels
 @pytest.mark.parametrize("E", [16, 32, 80])   # 32 and more local experts: the geometric pipeline schedule
 def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, pull_mode, native):
     from moe_explore.expert_compute import expert_compute

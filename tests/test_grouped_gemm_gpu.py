@@ -214,12 +214,12 @@ def test_explicit_expert_ranges_cover_every_tile_exactly_once(native):
     native.gather_rows_peer(bases, p_rank, p_row, None, plan.num_mtiles, whole_a)
     whole = torch.zeros(plan.padded_rows, N // 2, dtype=torch.bfloat16, device="cuda")
     native.mgrouped_gemm(whole_a, w, whole, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, "swiglu", plan.status)
-    for bulk in (0, 16):
+    for bulk, dedicated in ((0, 0), (16, 0), (0, 8)):
         parts_a = torch.full_like(whole_a, 7.0)
         parts = torch.zeros_like(whole)
         for experts in ((0, 1), (1, 2), (2, 7), (7, 11)):
             native.gather_rows_peer(bases, p_rank, p_row, None, plan.num_mtiles, parts_a, plan.tile_pairs, E, experts=experts,
-                                    bulk_ctas=bulk, status=plan.status)
+                                    bulk_ctas=bulk, status=plan.status, dedicated_ctas=dedicated)
             native.mgrouped_gemm(parts_a, w, parts, None, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles, False, "swiglu",
                                  plan.status, options=native.gemm_options(experts=experts))
         plan.check()
