@@ -309,8 +309,10 @@ def run_ours(args):
             remap = balanced_placement(load.cpu(), world).to(device)
 
         if args.ep_mode == "peer":
-            ep_context = EPContext(dist.group.WORLD, w["T"], w["d"], w["k"], x.dtype, device)
-            ep_context.pull_mode = args.ep_pull
+            ep_context = EPContext(dist.group.WORLD, w["T"], w["d"], w["k"], x.dtype, device,
+                                   dispatch="dma" if args.ep_pull == "dma" else "pull")
+            if args.ep_pull != "dma":
+                ep_context.pull_mode = args.ep_pull
             if args.ep_reserved_sms is not None:
                 ep_context.reserved_sms = args.ep_reserved_sms
             if args.ep_chunks:
@@ -1019,7 +1021,7 @@ def main():
     ap.add_argument("--gather-in-gemm", default="auto", choices=["auto", "on", "off"],
                     help="single GPU: token rows gathered by the GEMMs' operand loads (auto = the package default) or "
                          "copied into the expert-sorted layout first")
-    ap.add_argument("--ep-pull", default="ldst", choices=["bulk", "ldst", "dedicated"],
+    ap.add_argument("--ep-pull", default="ldst", choices=["bulk", "ldst", "dedicated", "dma"],
                     help="N > 1, peer mode: pull rows with the copy-engine kernel on the reserved SMs or with the "
                          "load/store kernel on all SMs")
     ap.add_argument("--ep-reserved-sms", type=int, default=None,

@@ -196,6 +196,16 @@ int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank,
                          int chunk_count, void* dst, int64_t padded_rows, int cols, int dtype,
                          int bulk_ctas, int dedicated_ctas, int32_t* status, void* stream);
 
+/* Expert-parallel dispatch on the copy engines: `count` independent device-to-device copies (host arrays of
+ * destination addresses, source addresses -- typically blocks of peers' buffers -- and sizes), each issued as one
+ * plain asynchronous memcpy on `stream`.  When every source has sorted its rows by destination expert, the rows an
+ * expert receives from one source are one contiguous block on both sides, so the whole dispatch is E_local x ranks
+ * such copies and no SM touches a row.  moe_zero_padding_rows zeroes the rows of the padded layout that no copy
+ * fills (row_src < 0).  No counterpart in the reference. */
+int moe_copy_blocks(void* const* dst, const void* const* src, const size_t* bytes, int count, void* stream);
+int moe_zero_padding_rows(const int32_t* row_src, const int32_t* num_mtiles, void* dst,
+                          int64_t padded_rows, int cols, int dtype, void* stream);
+
 /* out[j, :] = src[dst_row[j], :] for j < R: padded layout back to flat-position order (zeros where
  * dst_row[j] < 0). */
 int moe_unpad_rows(const void* src, const int32_t* dst_row, void* out, int64_t num_rows,

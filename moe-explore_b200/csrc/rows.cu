@@ -353,6 +353,20 @@ __global__ void store_words_to_host_kernel(const unsigned long long* __restrict_
   __threadfence_system();
 }
 
+// Zeroes the padding rows (row_src < 0) of a [rows, vec_per_row] buffer in the padded layout: one warp per row.
+__global__ void __launch_bounds__(kRowThreads)
+zero_padding_rows_kernel(const int32_t* __restrict__ row_src, const int32_t* __restrict__ num_mtiles, uint4* __restrict__ dst,
+                         int vec_per_row) {
+  const int64_t rows_in_use = static_cast<int64_t>(*num_mtiles) * MOE_TILE_M;
+  const int warps = gridDim.x * (kRowThreads / 32);
+  const int lane = threadIdx.x & 31;
+  for (int64_t p = blockIdx.x * (kRowThreads / 32) + (threadIdx.x >> 5); p < rows_in_use; p += warps) {
+    if (row_src[p] >= 0) continue;
+    uint4* d = dst + p * vec_per_row;
+    for (int v = lane; v < vec_per_row; v += 32) d[v] = make_uint4(0, 0, 0, 0);
+  }
+}
+
 static int row_grid(int64_t rows) {
   const int64_t cap = static_cast<int64_t>(sm_count()) * 16;
   return static_cast<int>(rows < cap ? (rows > 0 ? rows : 1) : cap);
@@ -371,6 +385,29 @@ using namespace moe;
     return MOE_ERR_UNSUPPORTED;                                                                          \
   }                                                                                                      \
   MOE_CHECK_ARG((dtype) == MOE_DTYPE_BF16 || (dtype) == MOE_DTYPE_F16, name ": unknown dtype %d", (dtype))
+
+extern "C" int moe_zero_padding_rows(const int32_t* row_src, const int32_t* num_mtiles, void* dst, int64_t padded_rows,
+                                     int cols, int dtype, void* stream) {
+  MOE_CHECK_ARG(row_src && num_mtiles && dst, "moe_zero_padding_rows: null pointer argument");
+  MOE_CHECK_ARG(aligned16(dst) && padded_rows > 0, "moe_zero_padding_rows: dst must be 16-byte aligned, padded_rows positive");
+  MOE_ROW_COMMON_CHECKS("moe_zero_padding_rows", cols, dtype);
+  zero_padding_rows_kernel<<<sm_count() * 2, kRowThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      row_src, num_mtiles, static_cast<uint4*>(dst), cols / 8);
+  MOE_CUDA(cudaGetLastError());
+  return MOE_OK;
+}
+
+extern "C" int moe_copy_blocks(void* const* dst, const void* const* src, const size_t* bytes, int count, void* stream) {
+  MOE_CHECK_ARG(count >= 0 && (count == 0 || (dst && src && bytes)), "moe_copy_blocks: null pointer argument");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < count; ++i) {
+    if (bytes[i] == 0) continue;
+    MOE_CHECK_ARG(dst[i] != nullptr && src[i] != nullptr, "moe_copy_blocks: block %d has a null address", i);
+    // one plain asynchronous copy per block: the copy engines move it, no SM is involved
+    MOE_CUDA(cudaMemcpyAsync(dst[i], src[i], bytes[i], cudaMemcpyDeviceToDevice, s));
+  }
+  return MOE_OK;
+}
 
 extern "C" int moe_store_to_host(const void* src, void* dst_pinned_host, size_t bytes, void* stream) {
   MOE_CHECK_ARG(src != nullptr && dst_pinned_host != nullptr, "moe_store_to_host: null pointer argument");

@@ -52,6 +52,8 @@ SIGNATURES = {
     "moe_layout_from_groups": (c_int, [c_void_p, c_int64, c_int] + [c_void_p] * 7 + [c_void_p]),
     "moe_router_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "moe_store_to_host": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "moe_copy_blocks": (c_int, [POINTER(c_void_p), POINTER(c_void_p), POINTER(c_size_t), c_int, c_void_p]),
+    "moe_zero_padding_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                                      c_void_p, c_void_p]),
@@ -286,6 +288,27 @@ def read_small(values: torch.Tensor) -> list:
     _count(1)
     torch.cuda.current_stream().synchronize()
     return host[: flat.numel()].tolist()
+
+
+def copy_blocks(dst_addresses, src_addresses, sizes) -> None:
+    """One asynchronous device-to-device memcpy per (destination address, source address, bytes) triple, on the
+    current stream (copy engines; sources may be peers' buffers)."""
+    n = len(sizes)
+    if n == 0:
+        return
+    with timed("rows:copy_blocks"):
+        rc = load().moe_copy_blocks((c_void_p * n)(*dst_addresses), (c_void_p * n)(*src_addresses), (c_size_t * n)(*sizes), n,
+                                    _stream())
+    _check("moe_copy_blocks", rc)
+
+
+def zero_padding_rows(row_src, num_mtiles, dst) -> None:
+    """dst[p] = 0 for the padding rows (row_src[p] < 0) of a buffer in the padded layout."""
+    require_cuda(dst)
+    rc = load().moe_zero_padding_rows(_ptr(row_src), _ptr(num_mtiles), _ptr(dst), dst.size(0), dst.size(1),
+                                      dtype_code(dst.dtype), _stream())
+    _check("moe_zero_padding_rows", rc)
+    _count(1)
 
 
 def gather_rows(src, row_src, num_mtiles, dst, div):

@@ -16,7 +16,10 @@ Two data paths implement the exchanges:
     they need straight into the padded expert-sorted layout with the library's gather kernel (loads
     over NVLink), and the down-projection / dX grouped GEMMs PUSH every output row into the token
     owner's buffer from their epilogue (stores over NVLink, overlapped with the next tile's math).
-    Only row metadata (8 bytes per routed row) and three tiny barriers go through NCCL.
+    Only row metadata (8 bytes per routed row) and three tiny barriers go through NCCL.  A variant of the
+    dispatch (``EPContext(..., dispatch="dma")``) keeps the SMs out of it: every rank sorts its rows by destination
+    expert into a peer-mapped send buffer, and the owners fetch each (expert, source rank) block -- contiguous on
+    both sides -- with one asynchronous memcpy on the copy engines.
   * collective mode: rows are exchanged with ``all_to_all_single`` (NCCL) before and after the local
     GEMMs; kept as the baseline the peer path is measured against.
 
@@ -265,13 +268,17 @@ class EPContext:
     owners push back, in this rank's expert-sorted order.  A context serves one forward/backward pair
     at a time: ``y_back`` is read again by the backward pass."""
 
-    def __init__(self, group, num_tokens: int, hidden: int, topk: int, dtype, device, allocate=True):
+    def __init__(self, group, num_tokens: int, hidden: int, topk: int, dtype, device, allocate=True, dispatch="pull"):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.num_tokens, self.hidden, self.topk, self.dtype, self.device = num_tokens, hidden, topk, dtype, device
         self.rows_up = _round_up(max(num_tokens * topk, 1), 128)
         self.busy = False
+        # "pull": the owners' pull kernels read token rows from `src`; "dma": every rank sorts its rows by destination
+        # expert into `send` and the owners copy whole (expert, source) blocks with the copy engines
+        assert dispatch in ("pull", "dma")
+        self.dispatch = dispatch
         self.chunks = 8          # equal slices of the local expert list, used when `geometric` is off
         self.geometric = True    # slices cut by received rows, small first and growing (pipeline_schedule)
         self.comm_stream = None  # side stream the pulls run on (created with the buffers)
@@ -302,6 +309,9 @@ class EPContext:
             return t, handle, ptrs
 
         self.src, self._h_src, self.src_ptrs = make(self.num_tokens)
+        if self.dispatch == "dma":
+            self.send, self._h_send, self.send_ptrs = make(self.rows_up)
+            self.send_addresses = [int(p) for p in self._h_send.buffer_ptrs]   # host copy of the peers' base addresses
         self.y_back, self._h_y, self.y_ptrs = make(self.rows_up)
         self.dx_back, self._h_dx, self.dx_ptrs = make(self.rows_up)
         self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -321,11 +331,16 @@ class PeerLayout:
     p_scale: torch.Tensor         # fp32  [RP]: router weight of the row (applied to dOut rows in backward)
     num_received: int
     expert_rows: list = None      # rows received per local expert (host list; drives the pipeline schedule)
+    counts: list = None           # "dma" dispatch: counts[s][g] rows rank s routes to global expert position g (host)
 
 
-def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: int, group, ops) -> PeerLayout:
+def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: int, group, ops, after_sort=None,
+                      want_counts: bool = False) -> PeerLayout:
     """Exchange the row metadata of one routing decision: an all-gather of per-expert counts, one host
-    read of the split sizes, and an all-to-all of (token index, router weight) per routed row."""
+    read of the split sizes, and an all-to-all of (token index, router weight) per routed row.
+    ``after_sort(perm)`` runs right after the local sort and BEFORE the collectives (which then order whatever it
+    enqueued ahead of every peer's later reads); ``want_counts`` also brings the full [ranks, experts] count table to
+    the host."""
     world, me = dist.get_world_size(group), dist.get_rank(group)
     assert num_experts % world == 0, "experts must divide evenly over the ranks"
     e_local = num_experts // world
@@ -333,17 +348,24 @@ def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: 
     flat = indices.reshape(-1)
     R, dev = flat.numel(), flat.device
     perm, counts = ops.sort_by_expert(flat, num_experts)
+    if after_sort is not None:
+        after_sort(perm)
     gathered = torch.empty(world * num_experts, dtype=torch.int64, device=dev)
     dist.all_gather_into_tensor(gathered, counts.contiguous(), group=group)
     all_counts = gathered.view(world, num_experts)
     pair = all_counts.view(world, world, e_local).sum(-1)              # [source, owner] rows
     status = ops.status_word(dev).to(torch.int64) if hasattr(ops, "status_word") else torch.zeros(1, dtype=torch.int64, device=dev)
     local_rows = all_counts[:, me * e_local:(me + 1) * e_local].sum(0)       # rows each local expert receives
-    host_all = _native.read_small(torch.cat((pair.reshape(-1), local_rows, status)))   # the one host read of the step
+    parts = (pair.reshape(-1), local_rows, all_counts.reshape(-1), status) if want_counts else (pair.reshape(-1), local_rows, status)
+    host_all = _native.read_small(torch.cat(parts))                        # the one host read of the step
     _report(int(host_all[-1]))                                             # e.g. an expert id out of range
     send_splits = host_all[me * world:(me + 1) * world]
     recv_splits = host_all[me:world * world:world]
     expert_rows = host_all[world * world:world * world + e_local]
+    host_counts = None
+    if want_counts:
+        base = world * world + e_local
+        host_counts = [host_all[base + s * num_experts: base + (s + 1) * num_experts] for s in range(world)]
     num_received = sum(recv_splits)
     send_base = pair.cumsum(1) - pair                                   # start of each owner's segment at the source
     base_on_source = send_base[:, me]                                   # [world]
@@ -383,7 +405,7 @@ def build_peer_layout(indices: torch.Tensor, scores: torch.Tensor, num_experts: 
     padded[:R] = perm.to(torch.int32)
     tiles = torch.full((1,), padded.numel() // 128, dtype=torch.int32, device=dev)
     return PeerLayout(padded, inv, tiles, plan, p_rank.contiguous(), p_tok.contiguous(), p_dest.contiguous(),
-                      p_scale.contiguous(), num_received, expert_rows)
+                      p_scale.contiguous(), num_received, expert_rows, host_counts)
 
 
 class NativePeerOps(NativeOps):
@@ -433,9 +455,76 @@ class NativePeerOps(NativeOps):
     @classmethod
     def _gemm_options(cls, ctx: EPContext, experts, last: bool):
         """Launch options of one pipeline slice: its experts, and ``ctx.reserved_sms`` SMs left free for the pulls of
-        the slices after it (the last slice has no pull beside it and takes every SM)."""
-        cap = max(cls._sm_count(ctx) - ctx.reserved_sms, 2) if (ctx.reserved_sms > 0 and not last) else 0
+        the slices after it (the last slice has no pull beside it and takes every SM; so does every slice when the
+        copy engines do the dispatch)."""
+        reserve = ctx.reserved_sms > 0 and not last and ctx.dispatch != "dma"
+        cap = max(cls._sm_count(ctx) - ctx.reserved_sms, 2) if reserve else 0
         return _native.gemm_options(max_ctas=cap, experts=experts)
+
+    def sort_into_send(self, ctx: EPContext, rows: torch.Tensor, perm: torch.Tensor, scores=None):
+        """ctx.send[r] = rows[perm[r] // topk] (times scores.flat[perm[r]] when given): this rank's rows in expert
+        order, i.e. grouped by destination, for the owners' block copies."""
+        R = perm.numel()
+        tok = torch.full((ctx.rows_up,), -1, dtype=torch.int32, device=rows.device)
+        tok[:R] = torch.div(perm, ctx.topk, rounding_mode="floor").to(torch.int32)
+        rank0 = torch.where(tok >= 0, 0, -1).to(torch.int32)
+        scale = None
+        if scores is not None:
+            scale = torch.zeros(ctx.rows_up, dtype=torch.float32, device=rows.device)
+            scale[:R] = scores.reshape(-1)[perm].float()
+        # (filled by kernels with scalar arguments: a host-to-device memcpy of a few bytes would queue on a copy
+        # engine behind any large upload another stream has in flight)
+        base = torch.full((1,), rows.data_ptr(), dtype=torch.int64, device=rows.device)
+        tiles = torch.zeros(4, dtype=torch.int32, device=rows.device)
+        tiles[0] = ctx.rows_up // 128
+        with _native.timed("ep:sort_into_send"):
+            _native.gather_rows_peer(base, rank0, tok, scale, tiles, ctx.send)
+        ctx._send_keepalive = (rows, base)   # the kernel reads them asynchronously
+
+    def _dma_chunks(self, ctx: EPContext, lay: PeerLayout, dst):
+        """Enqueue, slice by slice on the side stream, the block copies that fill ``dst`` (padded expert-sorted rows)
+        from every rank's send buffer; returns one event per slice.  Expert e of this rank receives
+        counts[s][g] rows from rank s (g = its global position); they start at the sum of counts[s][:g] in that
+        rank's send buffer and, here, after the rows of the ranks before s inside the expert's padded segment."""
+        plan, chunks = lay.plan, self._chunks(ctx, lay)
+        world, me, counts = ctx.world, ctx.rank, lay.counts
+        e_local = plan.num_experts
+        row_bytes = ctx.hidden * dst.element_size()
+        send_offset = []
+        for s in range(world):                       # first row of global expert g in rank s's send buffer
+            acc, offs = 0, []
+            for g in range(world * e_local):
+                offs.append(acc)
+                acc += counts[s][g]
+            send_offset.append(offs)
+        main = torch.cuda.current_stream()
+        ctx.comm_stream.wait_stream(main)
+        events = []
+        pad_row = 0
+        pads = []
+        for e in range(e_local):
+            pads.append(pad_row)
+            total = sum(counts[s][me * e_local + e] for s in range(world))
+            pad_row += (total + 127) // 128 * 128
+        with torch.cuda.stream(ctx.comm_stream):
+            _native.zero_padding_rows(plan.row_src, plan.num_mtiles, dst)
+            for lo, hi in chunks:
+                d_addr, s_addr, sizes = [], [], []
+                for e in range(lo, hi):
+                    g = me * e_local + e
+                    row = pads[e]
+                    for s in range(world):
+                        n = counts[s][g]
+                        if n:
+                            d_addr.append(dst.data_ptr() + row * row_bytes)
+                            s_addr.append(ctx.send_addresses[s] + send_offset[s][g] * row_bytes)
+                            sizes.append(n * row_bytes)
+                            row += n
+                _native.copy_blocks(d_addr, s_addr, sizes)
+                ev = torch.cuda.Event()
+                ev.record(ctx.comm_stream)
+                events.append(ev)
+        return events
 
     def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
         """Enqueue the pull of every chunk on the side stream; returns one event per chunk."""
@@ -467,7 +556,7 @@ class NativePeerOps(NativeOps):
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
         xs, hidden, pre_act = new(rp, d), new(rp, weight2.size(1)), new(rp, weight1.size(2))
         main = torch.cuda.current_stream()
-        events = self._pull_chunks(ctx, lay, None, xs)
+        events = self._dma_chunks(ctx, lay, xs) if ctx.dispatch == "dma" else self._pull_chunks(ctx, lay, None, xs)
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
@@ -485,7 +574,8 @@ class NativePeerOps(NativeOps):
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
         gs, d_pre = new(rp, d), new(rp, pre_act.size(1))
         main = torch.cuda.current_stream()
-        events = self._pull_chunks(ctx, lay, lay.p_scale, gs)      # score-scaled dOut rows
+        # score-scaled dOut rows: scaled by the owner's pull kernel, or already by the source ("dma" dispatch)
+        events = self._dma_chunks(ctx, lay, gs) if ctx.dispatch == "dma" else self._pull_chunks(ctx, lay, lay.p_scale, gs)
         for event, chunk in zip(events, chunks):
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
@@ -510,9 +600,15 @@ class PeerEPExpertCompute(torch.autograd.Function):
         if ep.busy:
             raise RuntimeError("this EPContext still holds the rows of a forward pass whose backward has not run")
         scores = scores.to(x.dtype).contiguous()
-        ops.publish(ep, x.contiguous())
+        x = x.contiguous()
+        dma = getattr(ep, "dispatch", "pull") == "dma"
+        if not dma:
+            ops.publish(ep, x)
         with _native.timed("ep:layout"):
-            lay = build_peer_layout(indices, scores, num_experts, ep.group, ops)   # its collectives follow the publish
+            # its collectives follow the publish (or the sort into the send buffer) and so order it before peers' reads
+            lay = build_peer_layout(indices, scores, num_experts, ep.group, ops,
+                                    after_sort=(lambda perm: ops.sort_into_send(ep, x, perm)) if dma else None,
+                                    want_counts=dma)
         state = ops.peer_forward(ep, lay, weight1, weight2, act)
         ops.barrier(ep)                                                          # every owner has pushed its rows
         out = ops.fold(ep.y_back, scores, lay.inv_perm32, T, topk)
@@ -528,7 +624,11 @@ class PeerEPExpertCompute(torch.autograd.Function):
         T, topk = grad_out.size(0), ep.topk
         grad_out = grad_out.contiguous()
         d_scores = ops.fold_bwd_scores(grad_out, scores, ep.y_back, lay.perm32_padded, lay.tiles, topk)
-        ops.publish(ep, grad_out)
+        if getattr(ep, "dispatch", "pull") == "dma":
+            R = T * topk
+            ops.sort_into_send(ep, grad_out, lay.perm32_padded[:R].long(), scores)   # score-scaled, in expert order
+        else:
+            ops.publish(ep, grad_out)
         ops.barrier(ep)                                                          # every rank's dOut is in place
         d_w1, d_w2 = ops.peer_backward(ep, lay, ctx.state, weight1, weight2, ctx.act)
         ops.barrier(ep)                                                          # every owner has pushed its dX rows

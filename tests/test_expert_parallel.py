@@ -217,7 +217,7 @@ def test_balanced_placement_is_a_permutation_and_evens_the_load():
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("pull_mode", ["bulk", "ldst", "dedicated"])   # the three pull kernels
+@pytest.mark.parametrize("pull_mode", ["bulk", "ldst", "dedicated", "dma"])   # three pull kernels, copy-engine dispatch
 @pytest.mark.parametrize("E", [16, 32, 80])   # 32 and more local experts: the geometric pipeline schedule
 def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, pull_mode, native):
     from moe_explore.expert_compute import expert_compute
@@ -236,8 +236,10 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, pull_mode
         scores = torch.softmax(top, -1).bfloat16()
         from moe_explore.expert_parallel import EPContext
 
-        context = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, torch.device("cuda", 0))
-        context.pull_mode = pull_mode
+        context = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, torch.device("cuda", 0),
+                            dispatch="dma" if pull_mode == "dma" else "pull")
+        if pull_mode != "dma":
+            context.pull_mode = pull_mode
         outs = []
         for mode in ("peer", "collective", "single"):
             leaves = [t.detach().clone().requires_grad_() for t in (x, scores, w1, w2)]
@@ -290,11 +292,12 @@ def _gpu_ep_worker(rank, world, port, queue):
         x, scores, idx, grad = [t.to(device) for t in problems[rank]]
         results = {}
         context = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, device)
-        for mode in ("peer", "collective"):
+        context_dma = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, device, dispatch="dma")
+        for mode in ("peer", "dma", "collective"):
             leaves = [x.clone().requires_grad_(), scores.clone().requires_grad_(),
                       w1[mine].to(device).requires_grad_(), w2[mine].to(device).requires_grad_()]
             out = ep_expert_compute(leaves[0], leaves[1], remap.to(device)[idx], leaves[2], leaves[3], E, "swiglu",
-                                    context=context if mode == "peer" else None)
+                                    context={"peer": context, "dma": context_dma, "collective": None}[mode])
             out.backward(grad)
             torch.cuda.synchronize()
             results[mode] = [out.detach().float().cpu()] + [t.grad.float().cpu() for t in leaves]
@@ -345,9 +348,10 @@ def test_two_gpu_ranks_both_modes_against_the_oracle(native):
     rel = lambda a, b: float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
     for r in range(world):
         results, mine = got[r]
-        for mode in ("peer", "collective"):
+        for mode in ("peer", "dma", "collective"):
             out, dx, ds, dw1, dw2 = results[mode]
             assert rel(out, refs[r][0]) <= 2e-2 and rel(dx, refs[r][1]) <= 2e-2 and rel(ds, refs[r][2]) <= 2e-2, mode
             assert rel(dw1, dw1_sum[mine]) <= 2e-2 and rel(dw2, dw2_sum[mine]) <= 2e-2, mode
-        for a, b in zip(results["peer"], results["collective"]):
-            assert torch.equal(a, b)    # same kernels on the same rows in the same order
+        for mode in ("peer", "dma"):
+            for a, b in zip(results[mode], results["collective"]):
+                assert torch.equal(a, b)    # same kernels on the same rows in the same order
