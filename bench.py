@@ -21,6 +21,7 @@ gradient -- at every N.
 from __future__ import annotations
 
 import argparse
+import datetime
 import json
 import os
 import subprocess
@@ -274,7 +275,8 @@ def run_ours(args):
     _native.load()
     _native.query_device(local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        # a collective that has not finished after five minutes never will: end the run instead of holding the GPUs
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(minutes=5))
 
     name = args.workload or ("mixtral_8x7b" if world == 1 else "deepseek_v3_ep")
     w = dict(WORKLOADS[name])

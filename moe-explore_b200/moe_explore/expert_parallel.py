@@ -482,49 +482,46 @@ class NativePeerOps(NativeOps):
         ctx._send_keepalive = (rows, base)   # the kernel reads them asynchronously
 
     def _dma_chunks(self, ctx: EPContext, lay: PeerLayout, dst):
-        """Enqueue, slice by slice on the side stream, the block copies that fill ``dst`` (padded expert-sorted rows)
-        from every rank's send buffer; returns one event per slice.  Expert e of this rank receives
-        counts[s][g] rows from rank s (g = its global position); they start at the sum of counts[s][:g] in that
-        rank's send buffer and, here, after the rows of the ranks before s inside the expert's padded segment."""
+        """Generator over the pipeline slices: each ``next()`` enqueues, on the side stream, the block copies that
+        fill one slice of ``dst`` (padded expert-sorted rows) from every rank's send buffer and yields the event
+        recorded after them.  (A generator, so that the caller can enqueue the copies of slice c+1 and then launch the
+        GEMMs of slice c: issuing a few hundred memcpys takes the host milliseconds, which must not hold up the
+        GPU.)  Expert e of this rank receives counts[s][g] rows from rank s (g = its global position); they start at
+        the sum of counts[s][:g] in that rank's send buffer and, here, after the rows of the ranks before s inside
+        the expert's padded segment."""
         plan, chunks = lay.plan, self._chunks(ctx, lay)
         world, me, counts = ctx.world, ctx.rank, lay.counts
         e_local = plan.num_experts
         row_bytes = ctx.hidden * dst.element_size()
-        send_offset = []
-        for s in range(world):                       # first row of global expert g in rank s's send buffer
-            acc, offs = 0, []
-            for g in range(world * e_local):
-                offs.append(acc)
-                acc += counts[s][g]
-            send_offset.append(offs)
+        first = me * e_local
+        send_offset = [sum(counts[s][:first]) for s in range(world)]   # first row of my experts in rank s's send buffer
         main = torch.cuda.current_stream()
         ctx.comm_stream.wait_stream(main)
-        events = []
-        pad_row = 0
-        pads = []
-        for e in range(e_local):
-            pads.append(pad_row)
-            total = sum(counts[s][me * e_local + e] for s in range(world))
-            pad_row += (total + 127) // 128 * 128
         with torch.cuda.stream(ctx.comm_stream):
             _native.zero_padding_rows(plan.row_src, plan.num_mtiles, dst)
-            for lo, hi in chunks:
-                d_addr, s_addr, sizes = [], [], []
-                for e in range(lo, hi):
-                    g = me * e_local + e
-                    row = pads[e]
-                    for s in range(world):
-                        n = counts[s][g]
-                        if n:
-                            d_addr.append(dst.data_ptr() + row * row_bytes)
-                            s_addr.append(ctx.send_addresses[s] + send_offset[s][g] * row_bytes)
-                            sizes.append(n * row_bytes)
-                            row += n
+        # Every copy goes to the one side stream.  (Spreading a slice's copies over four streams, to engage more than one
+        # copy engine, ended in a cross-rank stall between the copies and the next stream-ordered barrier on a
+        # two-GPU run -- NCCL's watchdog ended it -- so it is not done.)
+        pad_row = 0
+        for lo, hi in chunks:
+            d_addr, s_addr, sizes = [], [], []
+            for e in range(lo, hi):
+                g = first + e
+                row = pad_row
+                for s in range(world):
+                    n = counts[s][g]
+                    if n:
+                        d_addr.append(dst.data_ptr() + row * row_bytes)
+                        s_addr.append(ctx.send_addresses[s] + send_offset[s] * row_bytes)
+                        sizes.append(n * row_bytes)
+                        row += n
+                        send_offset[s] += n
+                pad_row += (row - pad_row + 127) // 128 * 128
+            with torch.cuda.stream(ctx.comm_stream):
                 _native.copy_blocks(d_addr, s_addr, sizes)
                 ev = torch.cuda.Event()
                 ev.record(ctx.comm_stream)
-                events.append(ev)
-        return events
+            yield ev
 
     def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
         """Enqueue the pull of every chunk on the side stream; returns one event per chunk."""
@@ -556,8 +553,10 @@ class NativePeerOps(NativeOps):
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
         xs, hidden, pre_act = new(rp, d), new(rp, weight2.size(1)), new(rp, weight1.size(2))
         main = torch.cuda.current_stream()
-        events = self._dma_chunks(ctx, lay, xs) if ctx.dispatch == "dma" else self._pull_chunks(ctx, lay, None, xs)
-        for event, chunk in zip(events, chunks):
+        events = self._dma_chunks(ctx, lay, xs) if ctx.dispatch == "dma" else iter(self._pull_chunks(ctx, lay, None, xs))
+        ahead = next(events)
+        for chunk in chunks:
+            event, ahead = ahead, next(events, None)     # the next slice's rows are on their way before this one computes
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
             opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), self._slice_rows(lay, chunk)
@@ -575,8 +574,10 @@ class NativePeerOps(NativeOps):
         gs, d_pre = new(rp, d), new(rp, pre_act.size(1))
         main = torch.cuda.current_stream()
         # score-scaled dOut rows: scaled by the owner's pull kernel, or already by the source ("dma" dispatch)
-        events = self._dma_chunks(ctx, lay, gs) if ctx.dispatch == "dma" else self._pull_chunks(ctx, lay, lay.p_scale, gs)
-        for event, chunk in zip(events, chunks):
+        events = self._dma_chunks(ctx, lay, gs) if ctx.dispatch == "dma" else iter(self._pull_chunks(ctx, lay, lay.p_scale, gs))
+        ahead = next(events)
+        for chunk in chunks:
+            event, ahead = ahead, next(events, None)
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
             opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), self._slice_rows(lay, chunk)

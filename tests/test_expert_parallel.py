@@ -5,6 +5,7 @@ by indexing, local expert compute by the oracle) and must reproduce the single-p
 input / score gradients per rank, and each rank's slice of the summed expert weight gradients.
 GPU part: a one-rank NCCL group through the native kernels equals the single-GPU path.
 """
+import datetime
 import os
 import socket
 
@@ -225,8 +226,14 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, pull_mode
     from moe_explore.routing_plan import build_routing_plan
 
     os.environ["MASTER_ADDR"] = "127.0.0.1"
-    os.environ["MASTER_PORT"] = str(_free_port())
-    dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    for attempt in range(3):      # the probed port can be taken again before the store binds it
+        os.environ["MASTER_PORT"] = str(_free_port())
+        try:
+            dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+            break
+        except dist.DistNetworkError:
+            if attempt == 2:
+                raise
     try:
         T, d, k, I = 999, 512, 4, 256
         g = torch.Generator(device="cuda").manual_seed(2)
@@ -269,7 +276,7 @@ def _gpu_ep_worker(rank, world, port, queue):
     os.environ["MASTER_PORT"] = str(port)
     torch.cuda.set_device(rank)
     device = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device, timeout=datetime.timedelta(minutes=3))
     try:
         from moe_explore.expert_parallel import EPContext, balanced_placement, ep_expert_compute
 
