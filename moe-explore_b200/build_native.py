@@ -11,8 +11,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "libmoe_sm100.so")
-SOURCES = ["api.cu", "routing.cu", "rows.cu", "router.cu", "grouped_gemm.cu", "gemm_inst_bf16_pair.cu", "gemm_inst_bf16_single.cu",
-           "gemm_inst_f16_pair.cu", "gemm_inst_f16_single.cu", "no_alloc.cu"]
+SOURCES = ["api.cu", "routing.cu", "rows.cu", "router.cu", "grouped_gemm.cu", "no_alloc.cu"] + \
+          [f"gemm_inst_{t}_{c}{g}.cu" for t in ("bf16", "f16") for c in ("pair", "single") for g in ("", "_gather")]
 HEADERS = [os.path.join(CSRC, "common.cuh"), os.path.join(CSRC, "gemm_kernel.cuh"),
            os.path.join(os.path.dirname(HERE), "include", "moe_sm100.h")]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]

@@ -5,7 +5,7 @@
 
 namespace moe {
 #define MOE_INST(BN, A_K, B_K, EPI, KG) \
-  template int launch<__half, BN, A_K, B_K, EPI, KG, 1>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, \
+  template int launch<__half, BN, A_K, B_K, EPI, KG, 1, false>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, \
                                                         const CUtensorMap&, GemmArgs, const LaunchParams&);
 #define MOE_INST_BN(BN)                        \
   MOE_INST(BN, true, false, EPI_ACT, false)     \

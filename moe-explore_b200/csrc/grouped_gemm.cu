@@ -6,17 +6,25 @@
 
 namespace moe {
 
-#define MOE_EXTERN(T, CTAS, BN, A_K, B_K, EPI, KG)                                                              \
-  extern template int launch<T, BN, A_K, B_K, EPI, KG, CTAS>(const CUtensorMap&, const CUtensorMap&, const CUtensorMap&, \
-                                                             const CUtensorMap&, GemmArgs, const LaunchParams&);
-#define MOE_EXTERN_BN(T, CTAS, BN)                    \
-  MOE_EXTERN(T, CTAS, BN, true, false, EPI_ACT, false)     \
-  MOE_EXTERN(T, CTAS, BN, true, false, EPI_GLU, false)     \
-  MOE_EXTERN(T, CTAS, BN, true, false, EPI_ACT_AUX, false) \
-  MOE_EXTERN(T, CTAS, BN, true, true, EPI_ACT, false)      \
-  MOE_EXTERN(T, CTAS, BN, true, true, EPI_ACT_AUX, false)  \
-  MOE_EXTERN(T, CTAS, BN, true, true, EPI_DGLU, false)     \
-  MOE_EXTERN(T, CTAS, BN, false, false, EPI_ACT, true)
+#define MOE_EXTERN(T, CTAS, BN, A_K, B_K, EPI, KG, GATHER)                                                       \
+  extern template int launch<T, BN, A_K, B_K, EPI, KG, CTAS, GATHER>(const CUtensorMap&, const CUtensorMap&,       \
+                                                                     const CUtensorMap&, const CUtensorMap&, GemmArgs, \
+                                                                     const LaunchParams&);
+// every variant without the row gather; with it, the variants the gathering entry points reach
+#define MOE_EXTERN_BN(T, CTAS, BN)                                \
+  MOE_EXTERN(T, CTAS, BN, true, false, EPI_ACT, false, false)     \
+  MOE_EXTERN(T, CTAS, BN, true, false, EPI_GLU, false, false)     \
+  MOE_EXTERN(T, CTAS, BN, true, false, EPI_ACT_AUX, false, false) \
+  MOE_EXTERN(T, CTAS, BN, true, true, EPI_ACT, false, false)      \
+  MOE_EXTERN(T, CTAS, BN, true, true, EPI_ACT_AUX, false, false)  \
+  MOE_EXTERN(T, CTAS, BN, true, true, EPI_DGLU, false, false)     \
+  MOE_EXTERN(T, CTAS, BN, false, false, EPI_ACT, true, false)     \
+  MOE_EXTERN(T, CTAS, BN, true, false, EPI_ACT, false, true)      \
+  MOE_EXTERN(T, CTAS, BN, true, false, EPI_GLU, false, true)      \
+  MOE_EXTERN(T, CTAS, BN, true, false, EPI_ACT_AUX, false, true)  \
+  MOE_EXTERN(T, CTAS, BN, true, true, EPI_ACT, false, true)       \
+  MOE_EXTERN(T, CTAS, BN, true, true, EPI_ACT_AUX, false, true)   \
+  MOE_EXTERN(T, CTAS, BN, false, false, EPI_ACT, true, true)
 #define MOE_EXTERN_ALL(T, CTAS) MOE_EXTERN_BN(T, CTAS, 128) MOE_EXTERN_BN(T, CTAS, 256)
 MOE_EXTERN_ALL(__nv_bfloat16, 2)
 MOE_EXTERN_ALL(__nv_bfloat16, 1)
@@ -189,6 +197,7 @@ template <typename T, int BN, int CTAS>
 static int mgrouped_dispatch(const void* a, const void* w, int64_t a_rows, int K, int N, int E, int w_transposed, int epi,
                              const GemmArgs& args, int dtype, const LaunchParams& lp) {
   CUtensorMap ta, tb;
+  const bool gather = args.a_row_src != nullptr;  // selects the kernel variant whose operand loads gather rows
   {
     const uint64_t dims[2] = {(uint64_t)K, (uint64_t)a_rows};
     const uint32_t box[2] = {BK, args.a_row_src != nullptr ? 1u : (uint32_t)BM};
@@ -217,13 +226,20 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t a_rows, int K
       int rc = make_tmap(&td, dtype, args.out, 2, dims, box);
       if (rc != MOE_OK) return rc;
     }
-    return w_transposed ? launch<T, BN, true, true, EPI_ACT, false, CTAS>(ta, tb, ta, td, args, lp)
-                        : launch<T, BN, true, false, EPI_ACT, false, CTAS>(ta, tb, ta, td, args, lp);
+    if (gather)
+      return w_transposed ? launch<T, BN, true, true, EPI_ACT, false, CTAS, true>(ta, tb, ta, td, args, lp)
+                          : launch<T, BN, true, false, EPI_ACT, false, CTAS, true>(ta, tb, ta, td, args, lp);
+    return w_transposed ? launch<T, BN, true, true, EPI_ACT, false, CTAS, false>(ta, tb, ta, td, args, lp)
+                        : launch<T, BN, true, false, EPI_ACT, false, CTAS, false>(ta, tb, ta, td, args, lp);
   } else if (epi == EPI_GLU) {
-    return launch<T, BN, true, false, EPI_GLU, false, CTAS>(ta, tb, ta, ta, args, lp);
+    return gather ? launch<T, BN, true, false, EPI_GLU, false, CTAS, true>(ta, tb, ta, ta, args, lp)
+                  : launch<T, BN, true, false, EPI_GLU, false, CTAS, false>(ta, tb, ta, ta, args, lp);
   } else if (epi == EPI_ACT_AUX) {
-    return w_transposed ? launch<T, BN, true, true, EPI_ACT_AUX, false, CTAS>(ta, tb, ta, ta, args, lp)
-                        : launch<T, BN, true, false, EPI_ACT_AUX, false, CTAS>(ta, tb, ta, ta, args, lp);
+    if (gather)
+      return w_transposed ? launch<T, BN, true, true, EPI_ACT_AUX, false, CTAS, true>(ta, tb, ta, ta, args, lp)
+                          : launch<T, BN, true, false, EPI_ACT_AUX, false, CTAS, true>(ta, tb, ta, ta, args, lp);
+    return w_transposed ? launch<T, BN, true, true, EPI_ACT_AUX, false, CTAS, false>(ta, tb, ta, ta, args, lp)
+                        : launch<T, BN, true, false, EPI_ACT_AUX, false, CTAS, false>(ta, tb, ta, ta, args, lp);
   }
   // EPI_DGLU (always with the transposed weight: dAct = g @ W2^T): the saved product and the result are moved by
   // tensor copies of 32-row x 64-column boxes
@@ -236,7 +252,7 @@ static int mgrouped_dispatch(const void* a, const void* w, int64_t a_rows, int K
     rc = make_tmap(&td, dtype, args.out, 2, dims, box);
     if (rc != MOE_OK) return rc;
   }
-  return launch<T, BN, true, true, EPI_DGLU, false, CTAS>(ta, tb, tc, td, args, lp);
+  return launch<T, BN, true, true, EPI_DGLU, false, CTAS, false>(ta, tb, tc, td, args, lp);
 }
 
 static int mgrouped_common(const char* name, const void* a, const void* w, void* out, const MExtras& x,
@@ -366,7 +382,8 @@ static int kgrouped_dispatch(const void* a, const void* b, int64_t a_rows, int64
     int rc = make_tmap(&td, dtype, args.out, 3, dims, box);
     if (rc != MOE_OK) return rc;
   }
-  return launch<T, BN, false, false, EPI_ACT, true, CTAS>(ta, tb, ta, td, args, lp);
+  return args.a_row_src != nullptr ? launch<T, BN, false, false, EPI_ACT, true, CTAS, true>(ta, tb, ta, td, args, lp)
+                                   : launch<T, BN, false, false, EPI_ACT, true, CTAS, false>(ta, tb, ta, td, args, lp);
 }
 
 static int kgrouped_common(const char* name, const void* a, int64_t gather_rows, const int32_t* gather_row_src,
