@@ -166,7 +166,17 @@ def _ep_worker(rank, world, port, T, d, E, k, I, skew, queue, peer=False):
 @pytest.mark.parametrize("peer", [False, True], ids=["collective", "peer"])
 @pytest.mark.parametrize("skew", [False, True])
 def test_two_gloo_ranks_match_single_process_oracle(skew, peer):
-    world, T, d, E, k, I = 2, 24, 16, 8, 2, 8
+    _gloo_ranks_against_the_oracle(2, skew, peer)
+
+
+def test_four_gloo_ranks_match_single_process_oracle():
+    """More than two ranks (two local experts each, skewed routing, peer mode): the host logic has no case that only
+    holds for a pair of ranks."""
+    _gloo_ranks_against_the_oracle(4, True, True)
+
+
+def _gloo_ranks_against_the_oracle(world, skew, peer):
+    T, d, E, k, I = 24, 16, 8, 2, 8
     ctx = mp.get_context("spawn")
     queue = ctx.Queue()
     port = _free_port()
