@@ -16,8 +16,8 @@ Configurations: Mixtral-8x7B (T=8192, d=4096, E=8, top-2, I=14336, linear router
 E=60, top-4, I=1408, logits + per-expert bias), the OLMoE-shaped stress layer (d=2048, E=64, top-8, I=1024) at
 T=8192 for the three router distributions and at T=65536 for the degenerate one, and the DeepSeek-V3 shape
 (d=7168, E=256, top-8, I=2048, Zipf(1.1) popularity) at T=4096 tokens.  Synthetic seeded inputs stand in for model
-activations and checkpoints.  The measured figures are also written to gpurun_out/parity_full.json when that folder
-exists.
+activations and checkpoints.  The measured figures are also written, as JSON, to the file that the environment
+variable MOE_PARITY_REPORT names, when it is set.
 """
 import json
 import math
@@ -26,7 +26,6 @@ import os
 import pytest
 import torch
 
-from conftest import ROOT
 from oracle import moe_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -144,9 +143,9 @@ def compare_with_oracle(name, x, grad, w1, w2, scores, idx, ours, block):
     for e in empty:
         assert int(dw1[e].abs().sum()) == 0 and int(dw2[e].abs().sum()) == 0, f"expert {e} has no rows"
     RESULTS[name] = dict(res, empty_experts=len(empty))
-    out_dir = os.path.join(ROOT, "gpurun_out")
-    if os.path.isdir(out_dir):
-        with open(os.path.join(out_dir, "parity_full.json"), "w") as f:
+    report = os.environ.get("MOE_PARITY_REPORT")
+    if report:
+        with open(report, "w") as f:
             json.dump(RESULTS, f, indent=1)
     for tensor, m in res.items():
         assert m["max_rel"] <= TOL, f"{name} {tensor}: max relative error {m['max_rel']:.3e}"
