@@ -243,7 +243,8 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  *                 never be reached: the documented way to exercise the time-out path)
  *   group_m       row units per scheduling group; 0 = default (12)
  *   align_experts 0 = library's choice, 1 / -1 = scheduling groups never / may span two experts
- *   single_cta    1 = one-SM kernels even when tile_pairs is given
+ *   single_cta    0 = library's choice (CTA pairs, unless the experts average at most one 128-row tile: one-SM
+ *                 kernels then stream the weights faster), 1 = one-SM kernels, -1 = CTA pairs
  *   separate_copies 1 = fetch every 64-column block of an N-contiguous operand tile with a copy of its own instead
  *                 of one copy over a blocked view of the matrix (which needs the column count to be a multiple
  *                 of 64 and is otherwise the default): for comparison measurements

@@ -437,6 +437,45 @@ def test_one_copy_per_operand_tile_equals_one_copy_per_column_block(N, native):
     assert relerr(outs[0][3], ref) <= TOL
 
 
+@pytest.mark.parametrize("T", [300, 1500])
+def test_cta_pair_and_one_cta_kernels_agree_bit_for_bit(T, native):
+    """Where the experts average at most one 128-row tile the library launches the one-CTA kernels by itself (T = 300:
+    50 rows per expert), otherwise CTA pairs (T = 1500); ``single_cta`` = -1 / 1 forces either.  Every output element
+    is accumulated over the same operands in the same order in both, so all three choices give identical bits: gate/up
+    with SwiGLU, plain, transposed weight, the fused SwiGLU backward, and the K-grouped weight gradient."""
+    plan, x, w, g = _small_problem(native, 77, T=T)
+    E, K, N = w.shape
+    rp = plan.padded_rows
+    n = int(plan.num_mtiles[0].item()) * 128
+    xs = torch.empty(rp, K, dtype=x.dtype, device="cuda")
+    native.dispatch_rows(x, plan.dst_row, plan.row_src, plan.num_mtiles, xs, 1)
+    wt = (torch.randn(E, N // 2, K, generator=g) * 0.05).to(torch.bfloat16).cuda()   # a weight used transposed
+    m = plan.mtile_expert, plan.tile_pairs, plan.num_mtiles
+    outs = []
+    for choice in (0, -1, 1):
+        opts = native.gemm_options(single_cta=choice)
+        h, pre = torch.zeros(rp, N // 2, dtype=x.dtype, device="cuda"), torch.zeros(rp, N, dtype=x.dtype, device="cuda")
+        native.mgrouped_gemm(xs, w, h, pre, *m, False, "swiglu", plan.status, options=opts)
+        y = torch.zeros(rp, N, dtype=x.dtype, device="cuda")
+        native.mgrouped_gemm(xs, w, y, None, *m, False, None, plan.status, options=opts)
+        back = torch.zeros(rp, K, dtype=x.dtype, device="cuda")
+        native.mgrouped_gemm(y, w, back, None, *m, True, None, plan.status, options=opts)
+        d_pre = torch.zeros(rp, N, dtype=x.dtype, device="cuda")
+        native.mgrouped_gemm_dglu(xs, wt, pre, d_pre, *m, "swiglu", plan.status, options=opts)
+        dw = torch.empty(E, K, N, dtype=x.dtype, device="cuda")
+        native.kgrouped_gemm(xs, y, dw, plan.pad_offsets, plan.status, options=opts)
+        outs.append((h[:n].clone(), pre[:n].clone(), y[:n].clone(), back[:n].clone(), d_pre[:n].clone(), dw))
+    plan.check()
+    for other in outs[1:]:
+        for a_, b_ in zip(outs[0], other):
+            assert torch.equal(a_, b_)
+    ref = torch.zeros(rp, N, device="cuda")
+    for e in range(E):
+        lo, hi = int(plan.pad_offsets[e]), int(plan.pad_offsets[e + 1])
+        ref[lo:hi] = xs[lo:hi].float() @ w[e].float()
+    assert relerr(outs[0][2], ref[:n]) <= TOL
+
+
 def test_metadata_built_for_another_row_bound_is_refused(native):
     """padded_rows must be the bound the metadata was built with: a caller that passes fewer rows is told so through
     the status word and nothing is computed from misread scheduling words."""
