@@ -183,7 +183,9 @@ int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* ro
  * rows are read with ordinary loads over NVLink.  scale (fp32, may be NULL) is applied in fp32.
  * chunk_count > 1 restricts the call to the rows of the experts [E*chunk_index/chunk_count,
  * E*(chunk_index+1)/chunk_count) (see moe_mgrouped_gemm); chunk_count < 0 selects the explicit expert range
- * [chunk_index, -chunk_count) instead; tile_pairs and num_experts are needed for either.
+ * [chunk_index, -chunk_count) instead; pair_end > pair_begin selects the rows of the row-tile pairs
+ * [pair_begin, pair_end) of the pair list (the slice moe_gemm_options.pair_begin / pair_end names); tile_pairs and
+ * num_experts are needed for all three.
  * bulk_ctas > 0 selects the copy-engine kernel on that many CTAs (one per SM that is free for it): every warp
  * moves whole rows with cp.async.bulk through a shared-memory slot, which keeps ~170 KB of remote reads in
  * flight per SM; bulk_ctas == 0 selects the load/store kernel: spread over all SMs in 128-thread CTAs that also fit
@@ -193,8 +195,9 @@ int moe_dispatch_rows(const void* src, const int32_t* dst_row, const int32_t* ro
 int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank,
                          const int32_t* src_row, const float* scale, const int32_t* num_mtiles,
                          const int32_t* tile_pairs, int num_experts, int chunk_index,
-                         int chunk_count, void* dst, int64_t padded_rows, int cols, int dtype,
-                         int bulk_ctas, int dedicated_ctas, int32_t* status, void* stream);
+                         int chunk_count, int pair_begin, int pair_end, void* dst, int64_t padded_rows,
+                         int cols, int dtype, int bulk_ctas, int dedicated_ctas, int32_t* status,
+                         void* stream);
 
 /* Expert-parallel dispatch on the copy engines: `count` independent device-to-device copies (host arrays of
  * destination addresses, source addresses -- typically blocks of peers' buffers -- and sizes), each issued as one
@@ -254,6 +257,10 @@ int moe_combine_bwd(const void* dout, const void* scores, const void* ys,
  *   expert_begin, expert_end  M-grouped kernels: when end > begin, process exactly the experts [begin, end) (needs
  *                 tile_pairs); overrides chunk_index / chunk_count.  Lets a caller cut the expert list into slices
  *                 of unequal size, e.g. by row counts
+ *   pair_begin, pair_end  M-grouped kernels: when end > begin, process exactly the row-tile pairs [begin, end) of the
+ *                 pair list (needs tile_pairs); overrides the expert range.  Slices of this kind may cut through an
+ *                 expert: what the expert-parallel pipeline needs when one expert holds most of a rank's rows.  Pair p
+ *                 of the list covers the 128-row tiles tile_pairs[p] & 0xFFFFF and, if bit 31 is set, the next one
  *   wave_counter  device word for the barrier's arrivals, zeroed by the call on `stream`; NULL = a slot of the
  *                 library's own ring (shared by all streams: a clash only costs a launch its barrier) */
 typedef struct moe_gemm_options {
@@ -267,6 +274,8 @@ typedef struct moe_gemm_options {
   int32_t lane_stores;
   int32_t expert_begin;
   int32_t expert_end;
+  int32_t pair_begin;
+  int32_t pair_end;
   uint32_t* wave_counter;
 } moe_gemm_options;
 

@@ -110,6 +110,8 @@ struct GemmArgs {
   int32_t chunk_count;  // pipeline row movement against the GEMM); count <= 1 = everything
   int32_t expert_begin;  // M-grouped: when expert_end > expert_begin, process exactly the experts [begin, end)
   int32_t expert_end;    // instead (slices of unequal size, e.g. chosen by row counts)
+  int32_t pair_begin;    // M-grouped: when pair_end > pair_begin, process exactly the row-tile pairs [begin, end) of
+  int32_t pair_end;      // the pair list instead (slices that may cut through an expert)
   int32_t align_experts;  // M-grouped CTA pairs: scheduling groups never span two experts
   uint32_t* wave_counter;  // non-null: workers start every work item together (grid-wide arrival counter, zeroed
                            // by the host before the launch)
@@ -190,6 +192,7 @@ struct SmemPlan {
 struct Window {
   int m_begin;  // first row unit (pair or tile) of the window
   int e0, e1;   // experts of the window (M-grouped)
+  int p_end;    // CTA pairs: one past the last pair of the window (a window may begin and end inside an expert)
 };
 
 // Number of (row unit, column tile) work items and the row-unit / column-tile counts.  A row unit is
@@ -200,6 +203,7 @@ __device__ __forceinline__ int total_tiles(const GemmArgs& args, int& mt, int& n
   win.m_begin = 0;
   win.e0 = 0;
   win.e1 = args.num_experts;
+  win.p_end = 0x7FFFFFFF;
   if (KG) {
     mt = (args.m_dim + BM * CTAS - 1) / (BM * CTAS);
     return args.num_experts * mt * nt;
@@ -212,15 +216,24 @@ __device__ __forceinline__ int total_tiles(const GemmArgs& args, int& mt, int& n
       mt = 0;
       return 0;
     }
-    if (args.expert_end > args.expert_begin) {
-      win.e0 = args.expert_begin;
-      win.e1 = args.expert_end < args.num_experts ? args.expert_end : args.num_experts;
-    } else if (args.chunk_count > 1) {
-      win.e0 = static_cast<int>(static_cast<long long>(args.num_experts) * args.chunk_index / args.chunk_count);
-      win.e1 = static_cast<int>(static_cast<long long>(args.num_experts) * (args.chunk_index + 1) / args.chunk_count);
-    }
     const int pairs = args.num_mtiles[1];
-    const int p0 = args.pair_prefix[win.e0], p1 = args.pair_prefix[win.e1];
+    int p0, p1;
+    if (args.pair_end > args.pair_begin) {
+      // an explicit range of the pair list; the experts it touches are found by the search in decode_tile
+      p0 = args.pair_begin < pairs ? args.pair_begin : pairs;
+      p1 = args.pair_end < pairs ? args.pair_end : pairs;
+    } else {
+      if (args.expert_end > args.expert_begin) {
+        win.e0 = args.expert_begin;
+        win.e1 = args.expert_end < args.num_experts ? args.expert_end : args.num_experts;
+      } else if (args.chunk_count > 1) {
+        win.e0 = static_cast<int>(static_cast<long long>(args.num_experts) * args.chunk_index / args.chunk_count);
+        win.e1 = static_cast<int>(static_cast<long long>(args.num_experts) * (args.chunk_index + 1) / args.chunk_count);
+      }
+      p0 = args.pair_prefix[win.e0];
+      p1 = args.pair_prefix[win.e1];
+    }
+    win.p_end = p1;
     if (CTAS == 2) {
       win.m_begin = p0;
       mt = p1 - p0;
@@ -257,7 +270,11 @@ __device__ __forceinline__ TileCoord decode_tile(int t, int mt, int nt, const Wi
       if ((__ldg(args.pair_prefix + mid) - base) * nt <= t) lo = mid; else hi = mid;
     }
     span_begin = __ldg(args.pair_prefix + lo);
-    span = __ldg(args.pair_prefix + lo + 1) - span_begin;
+    int span_end = __ldg(args.pair_prefix + lo + 1);
+    // a window given as a pair range may begin or end inside this expert: walk only its part of the expert
+    if (span_begin < base) span_begin = base;
+    if (span_end > win.p_end) span_end = win.p_end;
+    span = span_end - span_begin;
     t -= (span_begin - base) * nt;
   }
   // split the span into equal groups of at most args.group_m row units

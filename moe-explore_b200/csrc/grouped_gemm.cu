@@ -284,6 +284,10 @@ static int mgrouped_common(const char* name, const void* a, const void* w, void*
                 o.expert_end);
   args.expert_begin = o.expert_begin;
   args.expert_end = o.expert_end;
+  MOE_CHECK_ARG(o.pair_end <= o.pair_begin || (tile_pairs != nullptr && o.pair_begin >= 0),
+                "%s: the pair range [%d, %d) needs tile_pairs and begin >= 0", name, o.pair_begin, o.pair_end);
+  args.pair_begin = o.pair_begin;
+  args.pair_end = o.pair_end;
   args.mtile_expert = mtile_expert;
   args.tile_pairs = tile_pairs;
   args.mtiles_bound = static_cast<int32_t>(padded_rows / BM);

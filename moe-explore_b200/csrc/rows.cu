@@ -65,25 +65,39 @@ dispatch_rows_kernel(const uint4* __restrict__ src, const int32_t* __restrict__ 
 // Row window of a pull: everything, or the rows of the experts of chunk `chunk_index` of `chunk_count` (the same
 // slicing the grouped GEMMs use, so a caller can pipeline the pull of chunk c+1 against the GEMMs of chunk c).
 // False when the metadata was built for another padded row count.
-// chunk_count < 0 encodes an explicit expert range: experts [chunk_index, -chunk_count).
+// chunk_count < 0 encodes an explicit expert range: experts [chunk_index, -chunk_count).  pair_end > pair_begin selects
+// the rows of the row-tile pairs [pair_begin, pair_end) of the pair list instead (a slice that may cut through an expert).
+struct RowWindow {
+  int chunk_index, chunk_count;
+  int pair_begin, pair_end;
+};
 __device__ __forceinline__ bool peer_row_window(const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
-                                                int num_experts, int mtiles_bound, int chunk_index, int chunk_count,
+                                                int num_experts, int mtiles_bound, const RowWindow& w,
                                                 int64_t& row_begin, int64_t& row_end) {
+  const int chunk_index = w.chunk_index, chunk_count = w.chunk_count;
+  const bool by_pairs = w.pair_end > w.pair_begin;
   row_begin = 0;
   row_end = static_cast<int64_t>(num_mtiles[0]) * MOE_TILE_M;
-  if (chunk_count > 1 || chunk_count < 0) {
+  if (chunk_count > 1 || chunk_count < 0 || by_pairs) {
     if (num_mtiles[2] != mtiles_bound) return false;
     const int32_t* pair_prefix = tile_pairs + mtiles_bound;
     const int pairs = num_mtiles[1];
-    int e0, e1;
-    if (chunk_count < 0) {
-      e0 = chunk_index;
-      e1 = -chunk_count < num_experts ? -chunk_count : num_experts;
+    int p0, p1;
+    if (by_pairs) {
+      p0 = w.pair_begin < pairs ? w.pair_begin : pairs;
+      p1 = w.pair_end < pairs ? w.pair_end : pairs;
     } else {
-      e0 = static_cast<int>(static_cast<long long>(num_experts) * chunk_index / chunk_count);
-      e1 = static_cast<int>(static_cast<long long>(num_experts) * (chunk_index + 1) / chunk_count);
+      int e0, e1;
+      if (chunk_count < 0) {
+        e0 = chunk_index;
+        e1 = -chunk_count < num_experts ? -chunk_count : num_experts;
+      } else {
+        e0 = static_cast<int>(static_cast<long long>(num_experts) * chunk_index / chunk_count);
+        e1 = static_cast<int>(static_cast<long long>(num_experts) * (chunk_index + 1) / chunk_count);
+      }
+      p0 = pair_prefix[e0];
+      p1 = pair_prefix[e1];
     }
-    const int p0 = pair_prefix[e0], p1 = pair_prefix[e1];
     if (p1 < pairs) row_end = static_cast<int64_t>(tile_pairs[p1] & 0xFFFFF) * MOE_TILE_M;
     row_begin = p0 < pairs ? static_cast<int64_t>(tile_pairs[p0] & 0xFFFFF) * MOE_TILE_M : row_end;
   }
@@ -107,10 +121,10 @@ __global__ void __launch_bounds__(THREADS, THREADS == 128 ? 8 : 1)
 gather_rows_peer_kernel(const uint4* const* __restrict__ bases, const int32_t* __restrict__ src_rank,
                         const int32_t* __restrict__ src_row, const float* __restrict__ scale,
                         const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs,
-                        int num_experts, int mtiles_bound, int chunk_index, int chunk_count, uint4* __restrict__ dst,
+                        int num_experts, int mtiles_bound, RowWindow window, uint4* __restrict__ dst,
                         int vec_per_row) {
   int64_t row_begin, row_end;
-  if (!peer_row_window(num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count, row_begin, row_end)) return;
+  if (!peer_row_window(num_mtiles, tile_pairs, num_experts, mtiles_bound, window, row_begin, row_end)) return;
   // Two rows per iteration, up to four 16-byte loads per thread and row, ALL issued before the first store: a
   // remote load takes microseconds, so what a thread keeps in flight is what the pull is worth (with one row of
   // 7168 elements a thread had only 3.5 loads to issue; load -> store -> load in program order gave it one).
@@ -171,7 +185,7 @@ __global__ void __launch_bounds__(kBulkMaxWarps * 32)
 pull_rows_bulk_kernel(const uint4* const* __restrict__ bases, const int32_t* __restrict__ src_rank,
                       const int32_t* __restrict__ src_row, const float* __restrict__ scale,
                       const int32_t* __restrict__ num_mtiles, const int32_t* __restrict__ tile_pairs, int num_experts,
-                      int mtiles_bound, int chunk_index, int chunk_count, uint4* __restrict__ dst, int vec_per_row,
+                      int mtiles_bound, RowWindow window, uint4* __restrict__ dst, int vec_per_row,
                       long long wait_limit, int32_t* status) {
   extern __shared__ __align__(128) uint8_t slots_raw[];
   __shared__ __align__(8) uint64_t bars[kBulkMaxWarps];
@@ -187,7 +201,7 @@ pull_rows_bulk_kernel(const uint4* const* __restrict__ bases, const int32_t* __r
   }
   __syncwarp();
   int64_t row_begin, row_end;
-  if (!peer_row_window(num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count, row_begin, row_end)) return;
+  if (!peer_row_window(num_mtiles, tile_pairs, num_experts, mtiles_bound, window, row_begin, row_end)) return;
   uint32_t phase = 0;
   const int64_t stride = static_cast<int64_t>(gridDim.x) * warps;
   for (int64_t p = row_begin + static_cast<int64_t>(blockIdx.x) * warps + warp; p < row_end; p += stride) {
@@ -456,9 +470,9 @@ extern "C" int moe_dispatch_rows(const void* src, const int32_t* dst_row, const 
 
 extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t* src_rank, const int32_t* src_row,
                                     const float* scale, const int32_t* num_mtiles, const int32_t* tile_pairs,
-                                    int num_experts, int chunk_index, int chunk_count, void* dst,
-                                    int64_t padded_rows, int cols, int dtype, int bulk_ctas, int dedicated_ctas,
-                                    int32_t* status, void* stream) {
+                                    int num_experts, int chunk_index, int chunk_count, int pair_begin, int pair_end,
+                                    void* dst, int64_t padded_rows, int cols, int dtype, int bulk_ctas,
+                                    int dedicated_ctas, int32_t* status, void* stream) {
   MOE_CHECK_ARG(peer_bases && src_rank && src_row && num_mtiles && dst, "moe_gather_rows_peer: null pointer argument");
   MOE_CHECK_ARG(aligned16(dst), "moe_gather_rows_peer: dst must be 16-byte aligned");
   MOE_CHECK_ARG(padded_rows > 0, "moe_gather_rows_peer: bad sizes");
@@ -467,6 +481,9 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
                      (chunk_count > 1 ? chunk_index < chunk_count : chunk_index < -chunk_count && chunk_index < num_experts)),
                 "moe_gather_rows_peer: chunk %d of %d needs tile_pairs, num_experts and a valid slice", chunk_index,
                 chunk_count);
+  MOE_CHECK_ARG(pair_end <= pair_begin || (tile_pairs != nullptr && pair_begin >= 0),
+                "moe_gather_rows_peer: the pair range [%d, %d) needs tile_pairs and begin >= 0", pair_begin, pair_end);
+  const RowWindow window{chunk_index, chunk_count, pair_begin, pair_end};
   const int mtiles_bound = static_cast<int>(padded_rows / MOE_TILE_M);
   MOE_ROW_COMMON_CHECKS("moe_gather_rows_peer", cols, dtype);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -482,12 +499,12 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
       if (dtype == MOE_DTYPE_BF16) {
         MOE_CUDA(cudaFuncSetAttribute(pull_rows_bulk_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         pull_rows_bulk_kernel<__nv_bfloat16><<<grid_b, warps * 32, smem, s>>>(
-            bases, src_rank, src_row, scale, num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count,
+            bases, src_rank, src_row, scale, num_mtiles, tile_pairs, num_experts, mtiles_bound, window,
             static_cast<uint4*>(dst), cols / 8, wait_limit_cycles(), status);
       } else {
         MOE_CUDA(cudaFuncSetAttribute(pull_rows_bulk_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         pull_rows_bulk_kernel<__half><<<grid_b, warps * 32, smem, s>>>(
-            bases, src_rank, src_row, scale, num_mtiles, tile_pairs, num_experts, mtiles_bound, chunk_index, chunk_count,
+            bases, src_rank, src_row, scale, num_mtiles, tile_pairs, num_experts, mtiles_bound, window,
             static_cast<uint4*>(dst), cols / 8, wait_limit_cycles(), status);
       }
       MOE_CUDA(cudaGetLastError());
@@ -500,11 +517,10 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
     const int grid_d = dedicated_ctas < sm_count() ? dedicated_ctas : sm_count();
     if (dtype == MOE_DTYPE_BF16) {
       gather_rows_peer_kernel<__nv_bfloat16, 1024><<<grid_d, 1024, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
-                                                                         tile_pairs, num_experts, mtiles_bound, chunk_index,
-                                                                         chunk_count, static_cast<uint4*>(dst), cols / 8);
+                                                                         tile_pairs, num_experts, mtiles_bound, window, static_cast<uint4*>(dst), cols / 8);
     } else {
       gather_rows_peer_kernel<__half, 1024><<<grid_d, 1024, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
-                                                                  num_experts, mtiles_bound, chunk_index, chunk_count,
+                                                                  num_experts, mtiles_bound, window,
                                                                   static_cast<uint4*>(dst), cols / 8);
     }
     MOE_CUDA(cudaGetLastError());
@@ -516,11 +532,10 @@ extern "C" int moe_gather_rows_peer(const void* const* peer_bases, const int32_t
   const int grid = static_cast<int>(padded_rows < cap ? padded_rows : cap);
   if (dtype == MOE_DTYPE_BF16) {
     gather_rows_peer_kernel<__nv_bfloat16, 128><<<grid, 128, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles,
-                                                                    tile_pairs, num_experts, mtiles_bound, chunk_index,
-                                                                    chunk_count, static_cast<uint4*>(dst), cols / 8);
+                                                                    tile_pairs, num_experts, mtiles_bound, window, static_cast<uint4*>(dst), cols / 8);
   } else {
     gather_rows_peer_kernel<__half, 128><<<grid, 128, 0, s>>>(bases, src_rank, src_row, scale, num_mtiles, tile_pairs,
-                                                             num_experts, mtiles_bound, chunk_index, chunk_count,
+                                                             num_experts, mtiles_bound, window,
                                                              static_cast<uint4*>(dst), cols / 8);
   }
   MOE_CUDA(cudaGetLastError());

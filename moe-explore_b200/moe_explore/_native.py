@@ -30,7 +30,7 @@ class GemmOptions(ctypes.Structure):
     """``moe_gemm_options``: per-launch choices of the grouped GEMMs (zeros = the library's choices)."""
     _fields_ = [("max_ctas", c_int32), ("wave_sync", c_int32), ("wave_workers", c_int32), ("group_m", c_int32),
                 ("align_experts", c_int32), ("single_cta", c_int32), ("separate_copies", c_int32), ("lane_stores", c_int32),
-                ("expert_begin", c_int32), ("expert_end", c_int32),
+                ("expert_begin", c_int32), ("expert_end", c_int32), ("pair_begin", c_int32), ("pair_end", c_int32),
                 ("wave_counter", c_void_p)]
 
 
@@ -55,8 +55,8 @@ SIGNATURES = {
     "moe_copy_blocks": (c_int, [POINTER(c_void_p), POINTER(c_void_p), POINTER(c_size_t), c_int, c_void_p]),
     "moe_zero_padding_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_gather_rows": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
-    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int, c_int, c_int,
-                                     c_void_p, c_void_p]),
+    "moe_gather_rows_peer": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_int, c_int, c_void_p, c_int64, c_int, c_int,
+                                     c_int, c_int, c_void_p, c_void_p]),
     "moe_unpad_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "moe_combine_topk": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "moe_combine_bwd": (c_int, [c_void_p] * 7 + [c_int64, c_int, c_int64, c_int, c_int, c_void_p]),
@@ -198,10 +198,11 @@ def set_wait_limit_cycles(cycles: int) -> None:
 
 def gemm_options(max_ctas: int = 0, wave_sync: int = 0, wave_workers: int = 0, group_m: int = 0, align_experts: int = 0,
                  single_cta: int = 0, separate_copies: int = 0, lane_stores: int = 0, experts=(0, 0),
-                 wave_counter=None) -> GemmOptions:
-    """``experts`` = (begin, end): the M-grouped kernels process exactly that slice of the expert list."""
+                 wave_counter=None, pairs=(0, 0)) -> GemmOptions:
+    """``experts`` = (begin, end): the M-grouped kernels process exactly that slice of the expert list; ``pairs`` =
+    (begin, end): exactly that slice of the list of row-tile pairs (it may cut through an expert)."""
     return GemmOptions(max_ctas, wave_sync, wave_workers, group_m, align_experts, single_cta, separate_copies, lane_stores,
-                       int(experts[0]), int(experts[1]),
+                       int(experts[0]), int(experts[1]), int(pairs[0]), int(pairs[1]),
                        None if wave_counter is None else wave_counter.data_ptr())
 
 
@@ -321,17 +322,19 @@ def gather_rows(src, row_src, num_mtiles, dst, div):
 
 
 def gather_rows_peer(peer_bases, src_rank, src_row, scale, num_mtiles, dst, tile_pairs=None, num_experts=0,
-                     chunk=(0, 1), bulk_ctas: int = 0, status=None, experts=None, dedicated_ctas: int = 0):
+                     chunk=(0, 1), bulk_ctas: int = 0, status=None, experts=None, dedicated_ctas: int = 0, pairs=(0, 0)):
     """dst[p] = scale[p] * peer_bases[src_rank[p]][src_row[p]]; peer_bases: int64 device tensor of base pointers.
     ``bulk_ctas`` > 0: the copy-engine kernel on that many CTAs; 0: the load/store kernel, on all SMs or, with
     ``dedicated_ctas`` > 0, as that many 1024-thread CTAs that each take a whole SM.
-    ``experts`` = (begin, end) restricts the call to the rows of that slice of the expert list (else ``chunk``)."""
+    ``experts`` = (begin, end) restricts the call to the rows of that slice of the expert list (else ``chunk``);
+    ``pairs`` = (begin, end) to the rows of that slice of the list of row-tile pairs."""
     require_cuda(peer_bases, dst)
     if experts is not None:
         chunk = (int(experts[0]), -int(experts[1]))   # the C entry point's encoding of an explicit range
     with timed("rows:gather_peer"):
         rc = load().moe_gather_rows_peer(_ptr(peer_bases), _ptr(src_rank), _ptr(src_row), _ptr(scale), _ptr(num_mtiles),
-                                         _ptr(tile_pairs), num_experts, chunk[0], chunk[1], _ptr(dst), dst.size(0),
+                                         _ptr(tile_pairs), num_experts, chunk[0], chunk[1], int(pairs[0]), int(pairs[1]),
+                                         _ptr(dst), dst.size(0),
                                          dst.size(1), dtype_code(dst.dtype), int(bulk_ctas), int(dedicated_ctas),
                                          _ptr(status), _stream())
     _check("moe_gather_rows_peer", rc)

@@ -34,7 +34,7 @@ the CPU by itself.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import NamedTuple, Optional
 
 import torch
 import torch.distributed as dist
@@ -99,6 +99,24 @@ def pipeline_schedule(rows_per_expert, first_fraction: float = 1.0 / 32, growth:
             target = done * (1.0 + growth)
     slices.append((begin, n))
     return slices
+
+
+def pair_rows(rows_per_expert):
+    """Rows of every entry of the list of row-tile pairs the routing metadata builds for these per-expert row counts:
+    an expert with r rows has ceil(r / 128) tiles and ceil(tiles / 2) pairs of (at most) 256 rows."""
+    out = []
+    for r in rows_per_expert:
+        r = int(r)
+        pairs = ((r + 127) // 128 + 1) // 2
+        out.extend(min(256, r - 256 * p) for p in range(pairs))
+    return out
+
+
+class Slice(NamedTuple):
+    """One slice of a pass's pipeline: a range of the local expert list, or of the list of row-tile pairs."""
+    experts: tuple
+    pairs: tuple
+    rows: float
 
 
 class NativeOps:
@@ -281,6 +299,7 @@ class EPContext:
         self.dispatch = dispatch
         self.chunks = 8          # equal slices of the local expert list, used when `geometric` is off
         self.geometric = True    # slices cut by received rows, small first and growing (pipeline_schedule)
+        self.slice_pairs = True  # ... in the list of row-tile pairs, so that a slice may end inside an expert
         self.comm_stream = None  # side stream the pulls run on (created with the buffers)
         # SMs the grouped GEMMs leave free while rows are pulled from peers (read by the native ops): a pull CTA
         # that shares an SM with a GEMM CTA gets almost none of the SM's L2 ingress (measured at 2 ranks: 37.8 ms
@@ -442,6 +461,20 @@ class NativePeerOps(NativeOps):
         n = max(1, min(ctx.chunks, experts))
         return [(experts * c // n, experts * (c + 1) // n) for c in range(n) if experts * (c + 1) // n > experts * c // n]
 
+    @classmethod
+    def _slices(cls, ctx: EPContext, lay: PeerLayout):
+        """The pipeline slices of a pass, in launch order.  With the pull dispatch and known per-expert row counts they
+        are cut in the list of row-tile pairs, so that a slice may end inside an expert: under a skewed router one
+        expert can hold most of a rank's rows (93 % on the hottest rank of 8 with Zipf(1.1) popularity), and slices of
+        whole experts then leave its pull with nothing to hide behind.  Otherwise: whole experts (``_chunks``)."""
+        experts = lay.plan.num_experts
+        if (ctx.dispatch == "pull" and ctx.geometric and ctx.slice_pairs and lay.expert_rows is not None
+                and len(lay.expert_rows) == experts):
+            rows = pair_rows(lay.expert_rows)
+            if len(rows) > 1:
+                return [Slice((0, 0), (lo, hi), float(sum(rows[lo:hi]))) for lo, hi in pipeline_schedule(rows)]
+        return [Slice(chunk, (0, 0), cls._slice_rows(lay, chunk)) for chunk in cls._chunks(ctx, lay)]
+
     @staticmethod
     def _slice_rows(lay: PeerLayout, experts):
         if lay.expert_rows is None:
@@ -453,13 +486,13 @@ class NativePeerOps(NativeOps):
         return _native.query_device(ctx.device.index if ctx.device.index is not None else torch.cuda.current_device())[0]
 
     @classmethod
-    def _gemm_options(cls, ctx: EPContext, experts, last: bool):
-        """Launch options of one pipeline slice: its experts, and ``ctx.reserved_sms`` SMs left free for the pulls of
-        the slices after it (the last slice has no pull beside it and takes every SM; so does every slice when the
-        copy engines do the dispatch)."""
+    def _gemm_options(cls, ctx: EPContext, piece: Slice, last: bool):
+        """Launch options of one pipeline slice: its experts or pairs, and ``ctx.reserved_sms`` SMs left free for the
+        pulls of the slices after it (the last slice has no pull beside it and takes every SM; so does every slice
+        when the copy engines do the dispatch)."""
         reserve = ctx.reserved_sms > 0 and not last and ctx.dispatch != "dma"
         cap = max(cls._sm_count(ctx) - ctx.reserved_sms, 2) if reserve else 0
-        return _native.gemm_options(max_ctas=cap, experts=experts)
+        return _native.gemm_options(max_ctas=cap, experts=piece.experts, pairs=piece.pairs)
 
     def sort_into_send(self, ctx: EPContext, rows: torch.Tensor, perm: torch.Tensor, scores=None):
         """ctx.send[r] = rows[perm[r] // topk] (times scores.flat[perm[r]] when given): this rank's rows in expert
@@ -524,8 +557,8 @@ class NativePeerOps(NativeOps):
             yield ev
 
     def _pull_chunks(self, ctx: EPContext, lay: PeerLayout, scale, dst):
-        """Enqueue the pull of every chunk on the side stream; returns one event per chunk."""
-        plan, chunks = lay.plan, self._chunks(ctx, lay)
+        """Enqueue the pull of every slice on the side stream; returns one event per slice."""
+        plan, chunks = lay.plan, self._slices(ctx, lay)
         main = torch.cuda.current_stream()
         ctx.comm_stream.wait_stream(main)          # the layout arrays and the destination exist
         # copy-engine pull: one CTA per reserved SM while GEMMs hold the others; every SM when nothing is reserved
@@ -539,7 +572,8 @@ class NativePeerOps(NativeOps):
             for chunk in chunks:
                 _native.gather_rows_peer(ctx.src_ptrs, lay.p_rank, lay.p_tok, scale, plan.num_mtiles, dst,
                                          plan.tile_pairs, plan.num_experts, bulk_ctas=bulk_ctas, status=plan.status,
-                                         experts=chunk, dedicated_ctas=dedicated_ctas)
+                                         experts=chunk.experts if chunk.pairs[1] <= chunk.pairs[0] else None,
+                                         pairs=chunk.pairs, dedicated_ctas=dedicated_ctas)
                 ev = torch.cuda.Event()
                 ev.record(ctx.comm_stream)
                 events.append(ev)
@@ -548,7 +582,7 @@ class NativePeerOps(NativeOps):
     def peer_forward(self, ctx: EPContext, lay: PeerLayout, weight1, weight2, act):
         """Dispatch (pull) chunk c+1 on the side stream while the gate/up and down GEMMs of chunk c run; the
         down GEMM's epilogue pushes its rows to the token owners (combine)."""
-        plan, chunks = lay.plan, self._chunks(ctx, lay)
+        plan, chunks = lay.plan, self._slices(ctx, lay)
         rp, d = plan.padded_rows, ctx.hidden
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
         xs, hidden, pre_act = new(rp, d), new(rp, weight2.size(1)), new(rp, weight1.size(2))
@@ -559,7 +593,7 @@ class NativePeerOps(NativeOps):
             event, ahead = ahead, next(events, None)     # the next slice's rows are on their way before this one computes
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
-            opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), self._slice_rows(lay, chunk)
+            opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), chunk.rows
             _native.mgrouped_gemm(xs, weight1, hidden, pre_act, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
                                   False, act, plan.status, rows=rows, options=opts)
             _native.mgrouped_gemm_push(hidden, weight2, ctx.y_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,
@@ -568,7 +602,7 @@ class NativePeerOps(NativeOps):
 
     def peer_backward(self, ctx: EPContext, lay: PeerLayout, state, weight1, weight2, act):
         xs, hidden, pre_act = state
-        plan, chunks = lay.plan, self._chunks(ctx, lay)
+        plan, chunks = lay.plan, self._slices(ctx, lay)
         rp, d = plan.padded_rows, ctx.hidden
         new = lambda *s: torch.empty(*s, dtype=ctx.dtype, device=ctx.device)
         gs, d_pre = new(rp, d), new(rp, pre_act.size(1))
@@ -580,7 +614,7 @@ class NativePeerOps(NativeOps):
             event, ahead = ahead, next(events, None)
             with _native.timed("ep:wait_pull"):
                 main.wait_event(event)
-            opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), self._slice_rows(lay, chunk)
+            opts, rows = self._gemm_options(ctx, chunk, chunk is chunks[-1]), chunk.rows
             _native.mgrouped_gemm_dglu(gs, weight2, pre_act, d_pre, plan.mtile_expert, plan.tile_pairs, plan.num_mtiles,
                                        act, plan.status, rows=rows, options=opts)
             _native.mgrouped_gemm_push(d_pre, weight1, ctx.dx_ptrs, lay.p_rank, lay.p_dest, plan.mtile_expert,

@@ -185,10 +185,10 @@ def _gloo_ranks_against_the_oracle(world, skew, peer):
         p.start()
     results = {}
     for _ in range(world):
-        item = queue.get(timeout=60)
+        item = queue.get(timeout=240)
         results[item[0]] = item[1:]
     for p in procs:
-        p.join(timeout=60)
+        p.join(timeout=240)
         assert p.exitcode == 0
 
     w1, w2, per_rank = _make_problem(world, T, d, E, k, I, skew)
@@ -231,6 +231,18 @@ def test_balanced_placement_is_a_permutation_and_evens_the_load():
 @pytest.mark.parametrize("pull_mode", ["bulk", "ldst", "dedicated", "dma"])   # three pull kernels, copy-engine dispatch
 @pytest.mark.parametrize("E", [16, 32, 80])   # 32 and more local experts: the geometric pipeline schedule
 def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, pull_mode, native):
+    _single_rank_case(E, pull_mode, hot=False)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("pull_mode", ["ldst", "bulk"])
+def test_single_rank_group_with_a_hot_expert(pull_mode, native):
+    """Every token sends one of its slots to expert 1 (a quarter of all rows, 26 times an average expert): the pipeline
+    slices, cut in the list of row-tile pairs, begin and end inside that expert."""
+    _single_rank_case(80, pull_mode, hot=True)
+
+
+def _single_rank_case(E, pull_mode, hot):
     from moe_explore.expert_compute import expert_compute
     from moe_explore.expert_parallel import ep_expert_compute
     from moe_explore.routing_plan import build_routing_plan
@@ -249,7 +261,10 @@ def test_single_rank_group_on_native_kernels_equals_single_gpu_path(E, pull_mode
         g = torch.Generator(device="cuda").manual_seed(2)
         mk = lambda *s, std=1.0: (torch.randn(*s, generator=g, device="cuda") * std).bfloat16()
         x, w1, w2, grad = mk(T, d), mk(E, d, 2 * I, std=0.05), mk(E, I, d, std=0.05), mk(T, d)
-        top, idx = torch.topk(torch.randn(T, E, generator=g, device="cuda"), k, dim=-1, sorted=False)
+        logits = torch.randn(T, E, generator=g, device="cuda")
+        if hot:
+            logits[:, 1] += 10.0
+        top, idx = torch.topk(logits, k, dim=-1, sorted=False)
         scores = torch.softmax(top, -1).bfloat16()
         from moe_explore.expert_parallel import EPContext
 

@@ -226,6 +226,56 @@ def test_explicit_expert_ranges_cover_every_tile_exactly_once(native):
         assert torch.equal(parts_a[:n], whole_a[:n]) and torch.equal(parts[:n], whole[:n])
 
 
+@pytest.mark.parametrize("single_cta", [-1, 1])
+@pytest.mark.parametrize("align", [1, -1])
+def test_pair_ranges_cover_every_tile_exactly_once(align, single_cta, native):
+    """``moe_gemm_options.pair_begin / pair_end`` and the matching pair range of the peer pull: slices of the list of
+    row-tile pairs that begin and end INSIDE an expert (one expert holds most rows here).  The launches over a
+    partition of the pair list equal one launch over everything, bit for bit -- CTA-pair and one-CTA kernels,
+    scheduling groups aligned to experts or not, gate/up with SwiGLU, the transposed-weight GEMM and the fused SwiGLU
+    backward."""
+    from moe_explore.routing_plan import build_routing_plan
+
+    g = torch.Generator().manual_seed(9)
+    E, T, K, N = 7, 6000, 256, 512
+    idx = torch.randint(0, E, (T, 1), generator=g)
+    idx[torch.rand(T, generator=g) < 0.8] = 2      # expert 2 holds ~83 % of the rows
+    idx[idx == 5] = 4                              # an expert without rows
+    plan = build_routing_plan(idx.cuda(), E, 1)
+    n = int(plan.num_mtiles[0].item()) * 128
+    pairs = int(plan.num_mtiles[1].item())
+    src = torch.randn(T, K, generator=g).to(torch.bfloat16).cuda()
+    bases = torch.tensor([src.data_ptr()], dtype=torch.int64, device="cuda")
+    p_rank = torch.where(plan.row_src >= 0, 0, -1).to(torch.int32)
+    p_row = plan.row_src.clamp_min(0).contiguous()
+    w = (torch.randn(E, K, N, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    wt = (torch.randn(E, N // 2, K, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    m = plan.mtile_expert, plan.tile_pairs, plan.num_mtiles
+
+    def run(windows):
+        a = torch.full((plan.padded_rows, K), 7.0, dtype=torch.bfloat16, device="cuda")
+        h = torch.zeros(plan.padded_rows, N // 2, dtype=torch.bfloat16, device="cuda")
+        pre = torch.zeros(plan.padded_rows, N, dtype=torch.bfloat16, device="cuda")
+        back = torch.zeros(plan.padded_rows, K, dtype=torch.bfloat16, device="cuda")
+        d_pre = torch.zeros(plan.padded_rows, N, dtype=torch.bfloat16, device="cuda")
+        for window in windows:
+            opts = native.gemm_options(pairs=window, align_experts=align, single_cta=single_cta)
+            native.gather_rows_peer(bases, p_rank, p_row, None, plan.num_mtiles, a, plan.tile_pairs, E, pairs=window,
+                                    status=plan.status)
+            native.mgrouped_gemm(a, w, h, pre, *m, False, "swiglu", plan.status, options=opts)
+            native.mgrouped_gemm(pre, w, back, None, *m, True, None, plan.status, options=opts)
+            native.mgrouped_gemm_dglu(a, wt, pre, d_pre, *m, "swiglu", plan.status, options=opts)
+        plan.check()
+        return [t[:n].clone() for t in (a, h, pre, back, d_pre)]
+
+    whole = run([(0, 0)])
+    cuts = [0, 1, 2, 5, pairs // 2, pairs - 1, pairs + 3]      # the last window runs past the end of the list
+    parts = run(list(zip(cuts[:-1], cuts[1:])))
+    for x, y in zip(whole, parts):
+        assert torch.equal(x, y)
+    assert float(whole[1].float().abs().max()) > 0
+
+
 @pytest.mark.parametrize("limit", [2, 36, 140])
 def test_capped_grid_gives_the_same_result(limit, native):
     """``max_ctas`` of the launch options only changes how many persistent CTAs share the tiles (also for the long

@@ -134,6 +134,33 @@ def test_pipeline_schedule_is_cut_by_rows_not_by_expert_count():
     assert pipeline_schedule([100] * 64, first_fraction=1 / 32) [0] == (0, 2)
 
 
+def test_pipeline_slices_may_end_inside_a_hot_expert():
+    """With the pull dispatch the slices are ranges of the list of row-tile pairs: they cover every pair once, the
+    first one is small, and an expert that holds nearly all rows is cut into several slices instead of being the
+    whole last one."""
+    from types import SimpleNamespace
+
+    from moe_explore.expert_parallel import NativePeerOps, pair_rows
+
+    assert pair_rows([0, 1, 128, 129, 256, 257, 600]) == [1, 128, 129, 256, 256, 1, 256, 256, 88]
+    rows = [40, 0, 130, 300, 500, 900, 1200, 258000]            # 31 light experts' worth and one hot one, roughly
+    ctx = SimpleNamespace(dispatch="pull", geometric=True, slice_pairs=True, chunks=8)
+    lay = SimpleNamespace(plan=SimpleNamespace(num_experts=len(rows)), expert_rows=rows, num_received=sum(rows))
+    slices = NativePeerOps._slices(ctx, lay)
+    per_pair = pair_rows(rows)
+    assert slices[0].pairs[0] == 0 and slices[-1].pairs[1] == len(per_pair)
+    for a, b in zip(slices, slices[1:]):
+        assert a.pairs[1] == b.pairs[0] and a.pairs[1] > a.pairs[0]
+    assert abs(sum(s.rows for s in slices) - sum(rows)) < 1e-6
+    assert slices[0].rows <= sum(rows) / 32 + 256
+    assert len(slices) >= 4 and slices[-1].rows < 0.75 * sum(rows)      # whole experts would end with a 98 % slice
+    # whole-expert slices when asked for, or when the copy engines do the dispatch
+    ctx.slice_pairs = False
+    assert all(s.pairs == (0, 0) for s in NativePeerOps._slices(ctx, lay))
+    ctx.slice_pairs, ctx.dispatch = True, "dma"
+    assert all(s.pairs == (0, 0) for s in NativePeerOps._slices(ctx, lay))
+
+
 def test_status_codes_map_to_errors_and_warnings():
     """The Python view of a device status word: 0 is fine, the wave barrier's fall-back is a warning (the launch's
     results are valid), everything else raises."""
@@ -156,10 +183,11 @@ def test_status_codes_map_to_errors_and_warnings():
 def test_options_struct_matches_the_library(native):
     import ctypes
 
-    assert native.load().moe_gemm_options_size() == ctypes.sizeof(native.GemmOptions) == 48
+    assert native.load().moe_gemm_options_size() == ctypes.sizeof(native.GemmOptions) == 56
     o = native.gemm_options(max_ctas=140, wave_sync=-1, wave_workers=3)
     assert (o.max_ctas, o.wave_sync, o.wave_workers, o.group_m, o.align_experts, o.single_cta, o.separate_copies,
-            o.lane_stores, o.expert_begin, o.expert_end, o.wave_counter) == (140, -1, 3, 0, 0, 0, 0, 0, 0, 0, None)
+            o.lane_stores, o.expert_begin, o.expert_end, o.pair_begin, o.pair_end, o.wave_counter) == (
+        140, -1, 3, 0, 0, 0, 0, 0, 0, 0, 0, 0, None)
 
 
 def test_oracle_upcasts_narrower_weights_per_expert():
