@@ -320,6 +320,8 @@ def run_ours(args):
             if args.ep_chunks:
                 ep_context.chunks = args.ep_chunks
                 ep_context.geometric = False
+            if args.ep_slices != "auto":
+                ep_context.slice_pairs = args.ep_slices == "pairs"
 
     def routing_of(x_in):
         """The routing decision of one step (same ops as inside the step): scores [T,k], positions in the weights."""
@@ -1043,6 +1045,10 @@ def main():
                     help="N > 1: which experts each rank owns: evened out by measured load (default) or blocks of E/N")
     ap.add_argument("--ep-chunks", type=int, default=None,
                     help="N > 1, peer mode: slices of the local expert list the dispatch pull is pipelined in")
+    ap.add_argument("--ep-slices", default="auto", choices=["auto", "pairs", "experts"],
+                    help="N > 1, peer mode: pipeline slices cut in the list of row-tile pairs (a slice may end inside an "
+                         "expert), made of whole experts, or (default) the former only where one expert holds most of a "
+                         "rank's rows")
     ap.add_argument("--ep-mode", default="peer", choices=["peer", "collective"],
                     help="N > 1: rows over peer-mapped memory inside the kernels (default) or NCCL all-to-all")
     ap.add_argument("--router", default=None, choices=["logits", "logits_bias", "zipf", "zipf15", "degenerate"],

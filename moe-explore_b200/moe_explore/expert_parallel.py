@@ -299,7 +299,10 @@ class EPContext:
         self.dispatch = dispatch
         self.chunks = 8          # equal slices of the local expert list, used when `geometric` is off
         self.geometric = True    # slices cut by received rows, small first and growing (pipeline_schedule)
-        self.slice_pairs = True  # ... in the list of row-tile pairs, so that a slice may end inside an expert
+        # ... in the list of row-tile pairs, so that a slice may end inside an expert: True / False, or None = only when
+        # slices of whole experts would leave more than `hot_slice_fraction` of the rows to one slice
+        self.slice_pairs = None
+        self.hot_slice_fraction = 0.7
         self.comm_stream = None  # side stream the pulls run on (created with the buffers)
         # SMs the grouped GEMMs leave free while rows are pulled from peers (read by the native ops): a pull CTA
         # that shares an SM with a GEMM CTA gets almost none of the SM's L2 ingress (measured at 2 ranks: 37.8 ms
@@ -466,14 +469,21 @@ class NativePeerOps(NativeOps):
         """The pipeline slices of a pass, in launch order.  With the pull dispatch and known per-expert row counts they
         are cut in the list of row-tile pairs, so that a slice may end inside an expert: under a skewed router one
         expert can hold most of a rank's rows (93 % on the hottest rank of 8 with Zipf(1.1) popularity), and slices of
-        whole experts then leave its pull with nothing to hide behind.  Otherwise: whole experts (``_chunks``)."""
+        whole experts then leave its pull with nothing to hide behind.  ``ctx.slice_pairs``: True / False force the
+        choice, None (default) cuts inside experts only when whole experts would give one slice more than
+        ``ctx.hot_slice_fraction`` of the rows.  Otherwise: whole experts (``_chunks``)."""
         experts = lay.plan.num_experts
-        if (ctx.dispatch == "pull" and ctx.geometric and ctx.slice_pairs and lay.expert_rows is not None
+        whole = [Slice(chunk, (0, 0), cls._slice_rows(lay, chunk)) for chunk in cls._chunks(ctx, lay)]
+        if (ctx.dispatch == "pull" and ctx.geometric and ctx.slice_pairs is not False and lay.expert_rows is not None
                 and len(lay.expert_rows) == experts):
-            rows = pair_rows(lay.expert_rows)
-            if len(rows) > 1:
-                return [Slice((0, 0), (lo, hi), float(sum(rows[lo:hi]))) for lo, hi in pipeline_schedule(rows)]
-        return [Slice(chunk, (0, 0), cls._slice_rows(lay, chunk)) for chunk in cls._chunks(ctx, lay)]
+            total = max(float(sum(lay.expert_rows)), 1.0)
+            # (measured at 2 ranks, where whole experts leave 61 % to the last slice: cutting inside experts costs 1.5 %
+            # -- more of the GEMM work then runs beside a pull, on fewer SMs -- so it is done only where it is needed)
+            if ctx.slice_pairs or max(s.rows for s in whole) > ctx.hot_slice_fraction * total:
+                rows = pair_rows(lay.expert_rows)
+                if len(rows) > 1:
+                    return [Slice((0, 0), (lo, hi), float(sum(rows[lo:hi]))) for lo, hi in pipeline_schedule(rows)]
+        return whole
 
     @staticmethod
     def _slice_rows(lay: PeerLayout, experts):

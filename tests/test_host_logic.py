@@ -144,7 +144,7 @@ def test_pipeline_slices_may_end_inside_a_hot_expert():
 
     assert pair_rows([0, 1, 128, 129, 256, 257, 600]) == [1, 128, 129, 256, 256, 1, 256, 256, 88]
     rows = [40, 0, 130, 300, 500, 900, 1200, 258000]            # 31 light experts' worth and one hot one, roughly
-    ctx = SimpleNamespace(dispatch="pull", geometric=True, slice_pairs=True, chunks=8)
+    ctx = SimpleNamespace(dispatch="pull", geometric=True, slice_pairs=None, hot_slice_fraction=0.7, chunks=8)
     lay = SimpleNamespace(plan=SimpleNamespace(num_experts=len(rows)), expert_rows=rows, num_received=sum(rows))
     slices = NativePeerOps._slices(ctx, lay)
     per_pair = pair_rows(rows)
@@ -154,11 +154,16 @@ def test_pipeline_slices_may_end_inside_a_hot_expert():
     assert abs(sum(s.rows for s in slices) - sum(rows)) < 1e-6
     assert slices[0].rows <= sum(rows) / 32 + 256
     assert len(slices) >= 4 and slices[-1].rows < 0.75 * sum(rows)      # whole experts would end with a 98 % slice
-    # whole-expert slices when asked for, or when the copy engines do the dispatch
+    # whole-expert slices when asked for, when the copy engines do the dispatch, or when no expert dominates
     ctx.slice_pairs = False
     assert all(s.pairs == (0, 0) for s in NativePeerOps._slices(ctx, lay))
     ctx.slice_pairs, ctx.dispatch = True, "dma"
     assert all(s.pairs == (0, 0) for s in NativePeerOps._slices(ctx, lay))
+    ctx.slice_pairs, ctx.dispatch = None, "pull"
+    even = SimpleNamespace(plan=SimpleNamespace(num_experts=32), expert_rows=[1000 + 10 * i for i in range(32)], num_received=0)
+    assert all(s.pairs == (0, 0) for s in NativePeerOps._slices(ctx, even))
+    ctx.slice_pairs = True
+    assert all(s.experts == (0, 0) for s in NativePeerOps._slices(ctx, even))
 
 
 def test_status_codes_map_to_errors_and_warnings():
