@@ -326,6 +326,7 @@ def _gpu_ep_worker(rank, world, port, queue):
         x, scores, idx, grad = [t.to(device) for t in problems[rank]]
         results = {}
         context = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, device)
+        context.slice_pairs = True      # pipeline slices that may end inside an expert (pair ranges), across real peers
         context_dma = EPContext(dist.group.WORLD, T, d, k, torch.bfloat16, device, dispatch="dma")
         for mode in ("peer", "dma", "collective"):
             leaves = [x.clone().requires_grad_(), scores.clone().requires_grad_(),
