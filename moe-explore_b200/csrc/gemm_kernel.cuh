@@ -12,10 +12,11 @@
 //
 // Roles inside a CTA (320 threads, one CTA per SM):
 //   warp 0      : TMA producer  -- cp.async.bulk.tensor tile loads into a ring of shared-memory
-//                 stages (128-byte swizzle), signalled by mbarriers.  With a row map (`a_row_src`) the A
-//                 rows are GATHERED by the loads themselves: the 32 lanes issue one tile::gather4 copy
-//                 each (4 rows x 128 bytes), so the token rows of an expert never have to be copied into
-//                 the expert-sorted layout first;
+//                 stages (128-byte swizzle), signalled by mbarriers.  In the GATHER variants of the
+//                 template (a row map `a_row_src` is given) the A rows are GATHERED by the loads themselves:
+//                 the 32 lanes issue one tile::gather4 copy each (4 rows x 128 bytes), so the token rows of
+//                 an expert never have to be copied into the expert-sorted layout first.  A compile-time
+//                 variant because this loop has no slack for branches it does not take;
 //   warp 1      : MMA issuer    -- tcgen05.mma (128 x BN x 16 per CTA, fp32 accumulators in TMEM,
 //                 two accumulator stages) and tcgen05.commit;
 //                 both warps walk their loops with all 32 lanes (uniform control flow) and let one
