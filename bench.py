@@ -254,6 +254,28 @@ def parity_record(x, out, dx, idx, scores, weights, grad_out, router_weight=None
     return {"out": rel(out[sample], ref.detach()), "dx": rel(dx[sample], xs.grad), "tokens_checked": int(sample.numel())}
 
 
+def bind_to_gpu_cpus(device_index: int):
+    """Restrict this process to the CPU cores NVML reports as local to its GPU (reading NVML only; the affinity is a
+    property of this process).  Page-locked buffers allocated afterwards are first touched, and so placed, on that
+    socket's memory: with one rank per GPU on a two-socket host, buffers on the other socket send every host copy
+    over the inter-socket link.  Returns the number of cores kept, or None when nothing was changed."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+        handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, ((os.cpu_count() or 64) + 63) // 64)
+        local = {64 * i + b for i, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        keep = os.sched_getaffinity(0) & local
+        if keep and keep != os.sched_getaffinity(0):
+            os.sched_setaffinity(0, keep)
+            return len(keep)
+    except Exception:
+        pass
+    return None
+
+
 def run_ours(args):
     import torch.distributed as dist
 
@@ -272,6 +294,7 @@ def run_ours(args):
             raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    cpu_binding = bind_to_gpu_cpus(local_rank) if world > 1 and not args.no_cpu_binding else None
     _native.load()
     _native.query_device(local_rank)
     if world > 1:
@@ -430,6 +453,7 @@ def run_ours(args):
     e2e = None
     if not args.device_only:
         e2e = run_e2e(args, step, x, grad_out, sync_all)
+        e2e["cpu_binding"] = cpu_binding
 
     rows_per_rank = None
     if world > 1:
@@ -833,7 +857,8 @@ def report(args, name, w, world, ms, e2e, launches, tracer, clocks, with_router,
             "h2d_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world,
             "d2h_bytes_per_step": 2 * w["T"] * w["d"] * 2 * world,
             "rank0_h2d_ms": e2e["h2d_ms"], "rank0_d2h_ms": e2e["d2h_ms"],
-            "rank0_h2d_gbs": e2e["h2d_gbs"], "rank0_d2h_gbs": e2e["d2h_gbs"]},
+            "rank0_h2d_gbs": e2e["h2d_gbs"], "rank0_d2h_gbs": e2e["d2h_gbs"],
+            "rank0_cpu_cores_bound_to_gpu": e2e.get("cpu_binding")},
         "gpu_launches": launches,
         "parity": parity,
     }
@@ -1045,6 +1070,8 @@ def main():
                     help="N > 1: which experts each rank owns: evened out by measured load (default) or blocks of E/N")
     ap.add_argument("--ep-chunks", type=int, default=None,
                     help="N > 1, peer mode: slices of the local expert list the dispatch pull is pipelined in")
+    ap.add_argument("--no-cpu-binding", action="store_true",
+                    help="N > 1: do not restrict each rank to the CPU cores local to its GPU")
     ap.add_argument("--ep-slices", default="auto", choices=["auto", "pairs", "experts"],
                     help="N > 1, peer mode: pipeline slices cut in the list of row-tile pairs (a slice may end inside an "
                          "expert), made of whole experts, or (default) the former only where one expert holds most of a "
