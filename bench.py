@@ -867,7 +867,7 @@ def report(args, name, w, world, ms, e2e, launches, tracer, clocks, with_router,
     if world > 1:
         line["config"]["ep_pull"] = args.ep_pull
         line["config"]["ep_slices"] = args.ep_slices + (" (pair ranges where one slice of whole experts would hold "
-                                                        "more than 70 % of a rank's rows)" if args.ep_slices == "auto" else "")
+                                                        "more than 85 % of a rank's rows)" if args.ep_slices == "auto" else "")
     # roofline of the dominant kernel: the gate/up grouped GEMM (4*R*d*I FLOPs per launch)
     key = gate_up_key(tracer.sections)
     if key:

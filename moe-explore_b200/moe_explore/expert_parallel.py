@@ -302,7 +302,7 @@ class EPContext:
         # ... in the list of row-tile pairs, so that a slice may end inside an expert: True / False, or None = only when
         # slices of whole experts would leave more than `hot_slice_fraction` of the rows to one slice
         self.slice_pairs = None
-        self.hot_slice_fraction = 0.7
+        self.hot_slice_fraction = 0.85
         self.comm_stream = None  # side stream the pulls run on (created with the buffers)
         # SMs the grouped GEMMs leave free while rows are pulled from peers (read by the native ops): a pull CTA
         # that shares an SM with a GEMM CTA gets almost none of the SM's L2 ingress (measured at 2 ranks: 37.8 ms
@@ -477,7 +477,7 @@ class NativePeerOps(NativeOps):
         if (ctx.dispatch == "pull" and ctx.geometric and ctx.slice_pairs is not False and lay.expert_rows is not None
                 and len(lay.expert_rows) == experts):
             total = max(float(sum(lay.expert_rows)), 1.0)
-            # (measured at 2 ranks, where whole experts leave 61 % to the last slice: cutting inside experts costs 1.5 %
+            # (measured at 2 ranks, where whole experts leave 72 % to the last slice: cutting inside experts costs 1.5 %
             # -- more of the GEMM work then runs beside a pull, on fewer SMs -- so it is done only where it is needed)
             if ctx.slice_pairs or max(s.rows for s in whole) > ctx.hot_slice_fraction * total:
                 rows = pair_rows(lay.expert_rows)

@@ -273,7 +273,7 @@ def _single_rank_case(E, pull_mode, hot):
         if pull_mode != "dma":
             context.pull_mode = pull_mode
         if hot:
-            context.slice_pairs = True     # (by itself the context cuts inside experts only when one holds > 70 % of the rows)
+            context.slice_pairs = True     # (by itself the context cuts inside experts only when one slice of whole experts would hold > 85 % of the rows)
         outs = []
         for mode in ("peer", "collective", "single"):
             leaves = [t.detach().clone().requires_grad_() for t in (x, scores, w1, w2)]

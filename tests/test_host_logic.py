@@ -144,7 +144,7 @@ def test_pipeline_slices_may_end_inside_a_hot_expert():
 
     assert pair_rows([0, 1, 128, 129, 256, 257, 600]) == [1, 128, 129, 256, 256, 1, 256, 256, 88]
     rows = [40, 0, 130, 300, 500, 900, 1200, 258000]            # 31 light experts' worth and one hot one, roughly
-    ctx = SimpleNamespace(dispatch="pull", geometric=True, slice_pairs=None, hot_slice_fraction=0.7, chunks=8)
+    ctx = SimpleNamespace(dispatch="pull", geometric=True, slice_pairs=None, hot_slice_fraction=0.85, chunks=8)
     lay = SimpleNamespace(plan=SimpleNamespace(num_experts=len(rows)), expert_rows=rows, num_received=sum(rows))
     slices = NativePeerOps._slices(ctx, lay)
     per_pair = pair_rows(rows)
