@@ -48,6 +48,15 @@ def _check_against_oracle(idx, E):
     for t in per_expert:
         expect.append(expect[-1] + (t + 1) // 2)
     assert prefix == expect and prefix[-1] == num_pairs
+    # the host's view of the pair list (what the expert-parallel pipeline cuts its slices in) is the device's:
+    # as many entries, and for every pair the rows of the tiles it covers
+    from moe_explore.expert_parallel import pair_rows
+
+    counts = torch.bincount(idx.reshape(-1).cpu(), minlength=E).tolist()
+    host_pairs = pair_rows(counts)
+    assert len(host_pairs) == num_pairs
+    live = (row_src >= 0).view(-1, 128).sum(1).tolist()                   # routed rows of every tile in use
+    assert host_pairs == [live[info & 0xFFFFF] + (live[(info & 0xFFFFF) + 1] if (info >> 31) & 1 else 0) for info in pairs]
     assert torch.equal(plan.pad_offsets.cpu(), po)
     assert torch.equal(plan.row_src[: n * 128].cpu(), row_src)
     assert torch.equal(plan.dst_row.cpu(), dst_row)
