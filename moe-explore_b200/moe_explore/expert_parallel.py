@@ -469,7 +469,9 @@ class NativePeerOps(NativeOps):
         """The pipeline slices of a pass, in launch order.  With the pull dispatch and known per-expert row counts they
         are cut in the list of row-tile pairs, so that a slice may end inside an expert: under a skewed router one
         expert can hold most of a rank's rows (93 % on the hottest rank of 8 with Zipf(1.1) popularity), and slices of
-        whole experts then leave its pull with nothing to hide behind.  ``ctx.slice_pairs``: True / False force the
+        whole experts then leave its pull with nothing to hide behind.  (Measured on 8 GPUs the step came out the same
+        either way, 78-80 ms: the GEMMs that run beside the pulls lose what the pulls take, whichever they are.  The
+        pair ranges keep the GEMM stream from ever waiting on one huge pull.)  ``ctx.slice_pairs``: True / False force the
         choice, None (default) cuts inside experts only when whole experts would give one slice more than
         ``ctx.hot_slice_fraction`` of the rows.  Otherwise: whole experts (``_chunks``)."""
         experts = lay.plan.num_experts
